@@ -278,24 +278,27 @@ def apply_penalties(logits, rows, toks, counts, rep, freq, pres):
 
 
 # ---- blocks with norms on both sides, scaled rotary tables, general attention, recurrent mixers -----
-def postnorm_add_rmsnorm(x, y, post_weight, post_eps, mult, weight, eps, out_dtype, rows=None):
-    """x += mult * rms(y) * post_weight;  out = rms(x) * weight (for `rows` only, x untouched)."""
-    yf = _f(y)
-    add = mult * (yf * torch.rsqrt(yf.pow(2).mean(-1, keepdim=True) + post_eps) * post_weight)
+def postnorm_add_rmsnorm(x, y, post_weight, post_eps, mult, weight, eps, out_dtype, rows=None, copy=False):
+    """x += mult * rms(y) * post_weight;  out = rms(x) * weight, or x itself with `copy` (for `rows` only, x untouched)."""
+    add = None
+    if y is not None:
+        yf = _f(y)
+        add = mult * (yf * torch.rsqrt(yf.pow(2).mean(-1, keepdim=True) + post_eps) * post_weight)
     if rows is None:
-        x += add
+        if add is not None:
+            x += add
         src = x
     else:
-        src = x[rows.long()] + add[rows.long()]
+        src = x[rows.long()] + (add[rows.long()] if add is not None else 0.0)
     if weight is None:
-        return None
+        return src.to(out_dtype) if copy else None
     return (src * torch.rsqrt(src.pow(2).mean(-1, keepdim=True) + eps) * weight).to(out_dtype)
 
 
-def gated_group_rmsnorm(y, z, weight, eps, group, gate_first, out_dtype):
+def gated_group_rmsnorm(y, z, weight, eps, group, gate_first, out_dtype, gate="silu"):
     n, width = y.shape
     zf = _f(z)
-    gate = zf / (1.0 + torch.exp(-zf))
+    gate = torch.sigmoid(zf) if gate == "sigmoid" else zf / (1.0 + torch.exp(-zf))
     w = weight.repeat(width // weight.numel())
     v = y * gate if gate_first else y
     v = v.view(n, width // group, group)
@@ -314,9 +317,12 @@ def rope_cos_sin_scaled(positions, freq, mult):
 
 
 def qk_norm_rope_write_split(qkv, nh, nkv, dk, dv, q_weight, k_weight, eps, cos, sin, rot, interleaved, cache_layer,
-                             page_size, slot_mapping, status=None):
+                             page_size, slot_mapping, status=None, whole=False):
     n = qkv.shape[0]
     for t in range(n):
+        if whole:
+            inv_q = torch.rsqrt(_f(qkv[t, :nh * dk]).pow(2).mean() + eps)
+            inv_k = torch.rsqrt(_f(qkv[t, nh * dk:(nh + nkv) * dk]).pow(2).mean() + eps)
         for h in range(nh + 2 * nkv):
             is_q, is_k = h < nh, nh <= h < nh + nkv
             if is_q or is_k:
@@ -325,7 +331,9 @@ def qk_norm_rope_write_split(qkv, nh, nkv, dk, dv, q_weight, k_weight, eps, cos,
                 c0, d = (nh + nkv) * dk + (h - nh - nkv) * dv, dv
             v = _f(qkv[t, c0:c0 + d]).clone()
             w = q_weight if is_q else (k_weight if is_k else None)
-            if w is not None:
+            if w is not None and whole:
+                v = v * (inv_q if is_q else inv_k) * (w[h * dk:(h + 1) * dk] if is_q else w[(h - nh) * dk:(h - nh + 1) * dk])
+            elif w is not None:
                 v = v * torch.rsqrt(v.pow(2).mean() + eps) * w
             if (is_q or is_k) and cos is not None:
                 half = rot // 2
@@ -476,8 +484,10 @@ def state_space(xbc, dt, A_log, dt_bias, D, state, state_offset, state_slots, cu
     return out
 
 
-def embed_sinusoid(table, tokens, positions, freq, streams=1, status=None):
+def embed_sinusoid(table, tokens, positions, freq, streams=1, status=None, pos_table=None):
     x = _f(table[tokens.long()])
+    if pos_table is not None:
+        x = x + _f(pos_table[positions.long()])
     if freq is not None:
         ang = positions.to(torch.float32)[:, None] * freq[None, :]
         pe = torch.stack([torch.sin(ang), torch.cos(ang)], -1).reshape(x.shape[0], -1)[:, :x.shape[1]]
@@ -557,15 +567,24 @@ def relu_squared(x):
     return (torch.relu(_f(x)) ** 2).to(x.dtype)
 
 
-def moe_route(h, router, correction, experts, top, groups, keep):
+def moe_route(h, router, correction, experts, top, groups, keep, bias=None, score="softmax"):
     n = h.shape[0]
+    if score == "chosen":
+        ids = torch.zeros((n, top), dtype=torch.int32)
+        wts = torch.zeros((n, top), dtype=torch.float32)
+        for t in range(n):
+            z = router @ _f(h[t]) + (bias if bias is not None else 0.0)
+            order = sorted(range(z.numel()), key=lambda e: (-float(z[e]), e))[:top]
+            ids[t] = torch.tensor(order, dtype=torch.int32)
+            wts[t] = torch.softmax(z[order], 0)
+        return ids, wts, None
     outputs = router.shape[0]
     ids = torch.zeros((n, top), dtype=torch.int32)
     wts = torch.zeros((n, top), dtype=torch.float32)
     per = outputs // groups
     for t in range(n):
-        s = torch.softmax(router @ _f(h[t]), 0)
-        choice = s + correction
+        s = torch.softmax(router @ _f(h[t]) + (bias if bias is not None else 0.0), 0)
+        choice = s + (correction if correction is not None else 0.0)
         if groups > 1 and keep < groups:
             gs = choice.reshape(groups, per).max(1).values
             kept = sorted(range(groups), key=lambda g: (-float(gs[g]), g))[:keep]
@@ -578,7 +597,7 @@ def moe_route(h, router, correction, experts, top, groups, keep):
     return ids, wts, None
 
 
-def moe_experts(h, ids, wts, plan, w_up, w_down, shared=None):
+def moe_experts(h, ids, wts, plan, w_up, w_down, shared=None, gated=False):
     n, W = h.shape
     experts = 0 if w_up is None else w_up.shape[0]
     out = torch.zeros((n, W), dtype=torch.float32)
@@ -586,6 +605,10 @@ def moe_experts(h, ids, wts, plan, w_up, w_down, shared=None):
         for e, g in zip(ids[t].tolist(), wts[t].tolist()):
             if e >= experts:
                 out[t] += g * _f(h[t])
+            elif gated:
+                gu = _f(w_up[e]) @ _f(h[t])
+                hid = (gu[0::2] / (1.0 + torch.exp(-gu[0::2])) * gu[1::2]).to(h.dtype)
+                out[t] += g * (_f(w_down[e]) @ _f(hid))
             else:
                 hid = (torch.relu(_f(w_up[e]) @ _f(h[t])) ** 2).to(h.dtype)
                 out[t] += g * (_f(w_down[e]) @ _f(hid))
@@ -594,7 +617,74 @@ def moe_experts(h, ids, wts, plan, w_up, w_down, shared=None):
     return out.to(h.dtype)
 
 
-ALL = ["embed", "resolve_tokens", "sample_truncated", "add_rmsnorm", "add_residual", "add_residual_ss", "skinny_applies", "tc_applies", "few_rows_applies", "swiglu", "linear", "strict_fp32", "rope_cos_sin",
+def _logsigmoid(z):
+    return torch.clamp(z, max=0.0) - torch.log1p(torch.exp(-z.abs()))
+
+
+def matrix_memory(qkv, gates, gate_bias, cap, state, state_slots, cu_q, positions, nh, dk, dv, q_scale, floor_eps=1e-6,
+                  status=None, max_q=1):
+    n = qkv.shape[0]
+    out = torch.zeros((n, nh * dv), dtype=torch.float32)
+    nS, nn = nh * dk * dv, nh * dk
+    for s in range(cu_q.numel() - 1):
+        r0, r1 = int(cu_q[s]), int(cu_q[s + 1])
+        if r1 == r0:
+            continue
+        slot = int(state_slots[s])
+        S = state[slot, :nS].view(nh, dk, dv).clone()
+        nv = state[slot, nS:nS + nn].view(nh, dk).clone()
+        m = state[slot, nS + nn:nS + nn + nh].clone()
+        if int(positions[r0]) == 0:
+            S.zero_(); nv.zero_(); m.zero_()
+        for r in range(r0, r1):
+            row = _f(qkv[r])
+            a = gates[r] + (gate_bias if gate_bias is not None else 0.0)
+            for h in range(nh):
+                qv = row[h * dk:(h + 1) * dk] * q_scale
+                kv = row[nh * dk + h * dk:nh * dk + (h + 1) * dk]
+                vv = row[2 * nh * dk + h * dv:2 * nh * dk + (h + 1) * dv]
+                li = cap * torch.tanh(a[h] / cap)
+                lf = _logsigmoid(cap * torch.tanh(a[nh + h] / cap))
+                new = torch.maximum(lf + m[h], li)
+                keep, take = torch.exp(lf + m[h] - new), torch.exp(li - new)
+                S[h] = keep * S[h] + take * torch.outer(kv, vv)
+                nv[h] = keep * nv[h] + take * kv
+                m[h] = new
+                den = torch.maximum((nv[h] @ qv).abs(), torch.exp(-new)) + floor_eps
+                out[r, h * dv:(h + 1) * dv] = (S[h].t() @ qv) / den
+        state[slot, :nS] = S.reshape(-1)
+        state[slot, nS:nS + nn] = nv.reshape(-1)
+        state[slot, nS + nn:nS + nn + nh] = m
+    return out
+
+
+def gated_linear_attention(qkv, decay_logits, tau, state, state_slots, cu_q, positions, nh, dk, dv, q_scale, status=None,
+                           max_q=1):
+    n = qkv.shape[0]
+    out = torch.zeros((n, nh * dv), dtype=torch.float32)
+    nS = nh * dk * dv
+    for s in range(cu_q.numel() - 1):
+        r0, r1 = int(cu_q[s]), int(cu_q[s + 1])
+        if r1 == r0:
+            continue
+        slot = int(state_slots[s])
+        S = state[slot, :nS].view(nh, dk, dv).clone()
+        if int(positions[r0]) == 0:
+            S.zero_()
+        for r in range(r0, r1):
+            row = _f(qkv[r])
+            alpha = torch.exp(_logsigmoid(decay_logits[r]) / tau).view(nh, dk)
+            for h in range(nh):
+                qv = row[h * dk:(h + 1) * dk] * q_scale
+                kv = row[nh * dk + h * dk:nh * dk + (h + 1) * dk]
+                vv = row[2 * nh * dk + h * dv:2 * nh * dk + (h + 1) * dv]
+                S[h] = alpha[h][:, None] * S[h] + torch.outer(kv, vv)
+                out[r, h * dv:(h + 1) * dv] = S[h].t() @ qv
+        state[slot, :nS] = S.reshape(-1)
+    return out
+
+
+ALL = ["matrix_memory", "gated_linear_attention", "embed", "resolve_tokens", "sample_truncated", "add_rmsnorm", "add_residual", "add_residual_ss", "skinny_applies", "tc_applies", "few_rows_applies", "swiglu", "linear", "strict_fp32", "rope_cos_sin",
        "qk_norm_rope_write", "attention_splits", "paged_attention", "shortconv", "sample_rows",
        "apply_penalties", "postnorm_add_rmsnorm", "gated_group_rmsnorm", "scale_rows", "rope_cos_sin_scaled",
        "qk_norm_rope_write_split", "masked_attention_splits", "masked_attention", "causal_conv_silu", "gated_delta",

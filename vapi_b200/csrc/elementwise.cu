@@ -383,8 +383,10 @@ VAPI_EXPORT int vapi_swiglu(const void* g, void* out, int dtype, int rows, int f
 // A sublayer's output y, normed on its way into the stream, and the norm that reads the stream
 // next, in one pass over the row:
 //   x <- x + mult * (y * rsqrt(mean(y^2) + eps_post) * w_post);   out = x * rsqrt(mean(x^2) + eps) * w
-// (blocks that norm a sublayer on both sides and scale its contribution).  `w` null: only the
-// stream is updated.  With `rows` the output has one row per entry and x is left untouched.
+// (blocks that norm a sublayer on both sides and scale its contribution).  `y` null: nothing is pending.
+// `w` null: no norm follows; with `out` the row itself is handed on in T (a sublayer that reads the stream as
+// it is), without it only the stream is updated.  With `rows` the output has one row per entry and x is left
+// untouched.
 // One block per row; every sum is float.
 template <typename T>
 __global__ void postnorm_add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ y,
@@ -399,28 +401,31 @@ __global__ void postnorm_add_rmsnorm_kernel(float* __restrict__ x, const T* __re
     if (j >= n_out) return;
     const int row = rows ? rows[j] : j;
     float* xr = x + (size_t)row * hidden;
-    const T* yr = y + (size_t)row * hidden;
+    const T* yr = y ? y + (size_t)row * hidden : nullptr;
     float ssy = 0.f;
-    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+    for (int c = threadIdx.x; c < hidden && yr; c += blockDim.x) {
         const float v = to_f32(yr[c]);
         ssy += v * v;
     }
-    ssy = block_sum(ssy, red);
+    if (yr) ssy = block_sum(ssy, red);
     const float inv_y = rsqrtf(ssy / (float)hidden + eps_post);
     float ss = 0.f;
     for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
-        const float v = xr[c] + mult * (to_f32(yr[c]) * inv_y * w_post[c]);
-        if (write_x) xr[c] = v;
+        const float v = yr ? xr[c] + mult * (to_f32(yr[c]) * inv_y * w_post[c]) : xr[c];
+        if (write_x && yr) xr[c] = v;
         ss += v * v;
     }
-    if (!w) return;
-    ss = block_sum(ss, red);
-    const float inv = rsqrtf(ss / (float)hidden + eps);
+    if (!out) return;
+    float inv = 1.f;
+    if (w) {
+        ss = block_sum(ss, red);
+        inv = rsqrtf(ss / (float)hidden + eps);
+    }
     T* orow = out + (size_t)j * hidden;
     for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
         // each thread reads back what it wrote itself
-        const float v = write_x ? xr[c] : xr[c] + mult * (to_f32(yr[c]) * inv_y * w_post[c]);
-        orow[c] = from_f32<T>(v * inv * w[c]);
+        const float v = (write_x || !yr) ? xr[c] : xr[c] + mult * (to_f32(yr[c]) * inv_y * w_post[c]);
+        orow[c] = from_f32<T>(w ? v * inv * w[c] : v);
     }
 }
 
@@ -440,7 +445,7 @@ __global__ void postnorm_add_rmsnorm_vec_kernel(float* __restrict__ x, const T* 
     if (j >= n_out) return;
     const int row = rows ? rows[j] : j;
     float* xr = x + (size_t)row * hidden;
-    const T* yr = y + (size_t)row * hidden;
+    const T* yr = y ? y + (size_t)row * hidden : nullptr;
     const int h4 = hidden >> 2;
     float4 v[NORM_KMAX];
     float ssy = 0.f;
@@ -448,37 +453,49 @@ __global__ void postnorm_add_rmsnorm_vec_kernel(float* __restrict__ x, const T* 
     for (int k = 0; k < NORM_KMAX; ++k) {
         const int c = threadIdx.x + k * blockDim.x;
         v[k] = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (c < h4) {
+        if (c < h4 && yr) {
             v[k] = Pack4<T>::load(yr + 4 * c);
             ssy += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
         }
     }
-    ssy = block_sum(ssy, red);
+    if (yr) ssy = block_sum(ssy, red);
     const float inv_y = rsqrtf(ssy / (float)hidden + eps_post);
     float ss = 0.f;
 #pragma unroll
     for (int k = 0; k < NORM_KMAX; ++k) {
         const int c = threadIdx.x + k * blockDim.x;
         if (c < h4) {
-            const float4 xv = Pack4<float>::load(xr + 4 * c), wp = Pack4<float>::load(w_post + 4 * c);
-            v[k].x = xv.x + mult * (v[k].x * inv_y * wp.x);
-            v[k].y = xv.y + mult * (v[k].y * inv_y * wp.y);
-            v[k].z = xv.z + mult * (v[k].z * inv_y * wp.z);
-            v[k].w = xv.w + mult * (v[k].w * inv_y * wp.w);
-            if (write_x) Pack4<float>::store(xr + 4 * c, v[k]);
+            const float4 xv = Pack4<float>::load(xr + 4 * c);
+            if (yr) {
+                const float4 wp = Pack4<float>::load(w_post + 4 * c);
+                v[k].x = xv.x + mult * (v[k].x * inv_y * wp.x);
+                v[k].y = xv.y + mult * (v[k].y * inv_y * wp.y);
+                v[k].z = xv.z + mult * (v[k].z * inv_y * wp.z);
+                v[k].w = xv.w + mult * (v[k].w * inv_y * wp.w);
+                if (write_x) Pack4<float>::store(xr + 4 * c, v[k]);
+            } else {
+                v[k] = xv;
+            }
             ss += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
         }
     }
-    if (!w) return;
-    ss = block_sum(ss, red);
-    const float inv = rsqrtf(ss / (float)hidden + eps);
+    if (!out) return;
+    float inv = 1.f;
+    if (w) {
+        ss = block_sum(ss, red);
+        inv = rsqrtf(ss / (float)hidden + eps);
+    }
     T* orow = out + (size_t)j * hidden;
 #pragma unroll
     for (int k = 0; k < NORM_KMAX; ++k) {
         const int c = threadIdx.x + k * blockDim.x;
         if (c < h4) {
-            const float4 wv = Pack4<float>::load(w + 4 * c);
-            Pack4<T>::store(orow + 4 * c, make_float4(v[k].x * inv * wv.x, v[k].y * inv * wv.y, v[k].z * inv * wv.z, v[k].w * inv * wv.w));
+            if (w) {
+                const float4 wv = Pack4<float>::load(w + 4 * c);
+                Pack4<T>::store(orow + 4 * c, make_float4(v[k].x * inv * wv.x, v[k].y * inv * wv.y, v[k].z * inv * wv.z, v[k].w * inv * wv.w));
+            } else {
+                Pack4<T>::store(orow + 4 * c, v[k]);
+            }
         }
     }
 }
@@ -487,7 +504,8 @@ VAPI_EXPORT int vapi_postnorm_add_rmsnorm(float* x, const void* y, int dtype, co
                                           float mult, const float* w, float eps, const int* rows, void* out,
                                           int n_out, int hidden, cudaStream_t stream) {
     if (n_out <= 0) return 0;
-    if (hidden <= 0 || !w_post) return fail(-1, "postnorm_add_rmsnorm: hidden=%d or no weight", hidden);
+    if (hidden <= 0 || (y && !w_post)) return fail(-1, "postnorm_add_rmsnorm: hidden=%d or no weight", hidden);
+    if (!y && !out) return 0;
     if (w && !out) return fail(-1, "postnorm_add_rmsnorm: a following norm needs an output");
     const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
     const int write_x = rows ? 0 : 1;
@@ -518,7 +536,12 @@ VAPI_EXPORT int vapi_postnorm_add_rmsnorm(float* x, const void* y, int dtype, co
 // RMS norm over equal groups of a row, with a gate:  out = norm_g(y) * w * silu(z)  (gate_first 0)
 // or  out = norm_g(y * silu(z)) * w  (gate_first 1).  y is float [n, width] (what a recurrence
 // left), z is T with its own row stride, w has w_len elements and is indexed by column % w_len (one
-// weight per head size, or one per column).  One warp per (row, group).
+// weight per head size, or one per column).  `gate_first` carries two bits: bit 0 the order above, bit 1 the
+// gate's kind (0: silu(z), 2: sigmoid(z)).  One warp per (row, group).
+__device__ __forceinline__ float norm_gate(float zv, int sigmoid_gate) {
+    return sigmoid_gate ? 1.f / (1.f + expf(-zv)) : zv / (1.f + expf(-zv));
+}
+
 template <typename T>
 __global__ void gated_group_rmsnorm_kernel(const float* __restrict__ y, const T* __restrict__ z, long long z_stride,
                                            const float* __restrict__ w, int w_len, float eps, int gate_first,
@@ -528,6 +551,8 @@ __global__ void gated_group_rmsnorm_kernel(const float* __restrict__ y, const T*
     pdl_trigger();
     pdl_wait();
     const int groups = width / group;
+    const int sig = gate_first & 2;
+    gate_first &= 1;
     if (item >= (long long)n * groups) return;
     const int t = (int)(item / groups), g = (int)(item - (long long)t * groups);
     const float* yr = y + (size_t)t * width + (size_t)g * group;
@@ -537,7 +562,7 @@ __global__ void gated_group_rmsnorm_kernel(const float* __restrict__ y, const T*
         float v = yr[c];
         if (gate_first) {
             const float zv = to_f32(zr[c]);
-            v *= zv / (1.f + expf(-zv));
+            v *= norm_gate(zv, sig);
         }
         ss += v * v;
     }
@@ -546,7 +571,7 @@ __global__ void gated_group_rmsnorm_kernel(const float* __restrict__ y, const T*
     T* orow = out + (size_t)t * width + (size_t)g * group;
     for (int c = lane; c < group; c += 32) {
         const float zv = to_f32(zr[c]);
-        const float gate = zv / (1.f + expf(-zv));
+        const float gate = norm_gate(zv, sig);
         const float wv = w[(g * group + c) % w_len];
         const float v = gate_first ? (yr[c] * gate) * inv * wv : yr[c] * inv * wv * gate;
         orow[c] = from_f32<T>(v);
@@ -561,6 +586,8 @@ __global__ void gated_group_rmsnorm_wide_kernel(const float* __restrict__ y, con
     __shared__ float red[33];
     const int groups = width / group;
     const int t = blockIdx.x / groups, g = blockIdx.x - t * groups;
+    const int sig = gate_first & 2;
+    gate_first &= 1;
     pdl_trigger();
     pdl_wait();
     const float* yr = y + (size_t)t * width + (size_t)g * group;
@@ -570,7 +597,7 @@ __global__ void gated_group_rmsnorm_wide_kernel(const float* __restrict__ y, con
         float v = yr[c];
         if (gate_first) {
             const float zv = to_f32(zr[c]);
-            v *= zv / (1.f + expf(-zv));
+            v *= norm_gate(zv, sig);
         }
         ss += v * v;
     }
@@ -579,7 +606,7 @@ __global__ void gated_group_rmsnorm_wide_kernel(const float* __restrict__ y, con
     T* orow = out + (size_t)t * width + (size_t)g * group;
     for (int c = threadIdx.x; c < group; c += blockDim.x) {
         const float zv = to_f32(zr[c]);
-        const float gate = zv / (1.f + expf(-zv));
+        const float gate = norm_gate(zv, sig);
         const float wv = w[(g * group + c) % w_len];
         orow[c] = from_f32<T>(gate_first ? (yr[c] * gate) * inv * wv : yr[c] * inv * wv * gate);
     }

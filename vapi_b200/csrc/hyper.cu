@@ -23,6 +23,7 @@ constexpr int HC_MAX_STREAMS = 8;
 template <typename T>
 __global__ void embed_sinusoid_kernel(const T* __restrict__ table, const int* __restrict__ tokens,
                                       const int* __restrict__ positions, const float* __restrict__ freq,
+                                      const T* __restrict__ pos_table, int pos_rows,
                                       float* __restrict__ x, int n, int hidden, int vocab, int streams,
                                       int* __restrict__ status) {
     const int t = blockIdx.x;
@@ -36,6 +37,16 @@ __global__ void embed_sinusoid_kernel(const T* __restrict__ table, const int* __
     }
     const float p = (float)positions[t];
     const T* row = table + (size_t)tok * hidden;
+    // a learned position vector: row `position` of a second table, added as it is
+    const T* prow = nullptr;
+    if (pos_table) {
+        int pi = positions[t];
+        if (pi < 0 || pi >= pos_rows) {
+            if (threadIdx.x == 0 && status) atomicExch(status, 5);
+            pi = 0;
+        }
+        prow = pos_table + (size_t)pi * hidden;
+    }
     float* xr = x + (size_t)t * streams * hidden;
     for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
         float v = to_f32(row[c]);
@@ -43,24 +54,25 @@ __global__ void embed_sinusoid_kernel(const T* __restrict__ table, const int* __
             const float angle = p * freq[c >> 1];
             v += (c & 1) ? cosf(angle) : sinf(angle);
         }
+        if (prow) v += to_f32(prow[c]);
         for (int s = 0; s < streams; ++s) xr[(size_t)s * hidden + c] = v;
     }
 }
 
 VAPI_EXPORT int vapi_embed_sinusoid(const void* table, int dtype, const int* tokens, const int* positions,
-                                    const float* freq, float* x, int n, int hidden, int vocab, int streams, int* status,
-                                    cudaStream_t stream) {
+                                    const float* freq, const void* pos_table, int pos_rows, float* x, int n, int hidden,
+                                    int vocab, int streams, int* status, cudaStream_t stream) {
     if (n <= 0) return 0;
     if (hidden <= 0 || vocab <= 0 || streams < 1 || streams > HC_MAX_STREAMS)
         return fail(-1, "embed_sinusoid: hidden=%d vocab=%d streams=%d", hidden, vocab, streams);
     const int threads = hidden >= 1024 ? 256 : 128;
     cudaError_t e;
     if (dtype == VAPI_F32)
-        e = launch(embed_sinusoid_kernel<float>, n, threads, 0, stream, (const float*)table, tokens, positions, freq, x, n,
-                   hidden, vocab, streams, status);
+        e = launch(embed_sinusoid_kernel<float>, n, threads, 0, stream, (const float*)table, tokens, positions, freq,
+                   (const float*)pos_table, pos_rows, x, n, hidden, vocab, streams, status);
     else if (dtype == VAPI_BF16)
         e = launch(embed_sinusoid_kernel<__nv_bfloat16>, n, threads, 0, stream, (const __nv_bfloat16*)table, tokens, positions,
-                   freq, x, n, hidden, vocab, streams, status);
+                   freq, (const __nv_bfloat16*)pos_table, pos_rows, x, n, hidden, vocab, streams, status);
     else
         return fail(-2, "embed_sinusoid: unsupported dtype %d", dtype);
     return check_launch("embed_sinusoid", e);

@@ -1,0 +1,295 @@
+// Mixers whose state is a matrix per head that every token decays and adds an outer product to:
+//
+//   matrix memory (mLSTM), per head, with log gates li (input) and lf (forget) and a running maximum m:
+//       m' = max(lf + m, li);  keep = exp(lf + m - m');  take = exp(li - m')
+//       S <- keep S + take k v^T;   n <- keep n + take k;   o = S^T q / (max(|n . q|, exp(-m')) + floor_eps)
+//       li = cap tanh((a_i + b_i) / cap),   lf = logsigmoid(cap tanh((a_f + b_f) / cap))
+//   gated linear attention, per head, with a decay per key channel:
+//       S <- diag(alpha) S + k v^T;   o = S^T q;   alpha = sigmoid(z)^(1/tau) = exp(logsigmoid(z) / tau)
+//
+// q is multiplied by `q_scale` on its way in.  S is [rows, cols] (key size x value size), float, in the
+// request's state slot; the matrix memory keeps n [heads, rows] and m [heads] behind all heads' S.  Memory is
+// never cleared: a sequence whose first token of the step sits at position 0 starts from zeros (m from 0)
+// whatever its slot holds.  Gates, decays, their logarithms and exponentials, n, m and S are float whatever T is;
+// the gates' pre-activations come in as float.
+//
+// The decomposition is the one of the other recurrences of this package: a block owns one (sequence, head) and
+// a slice of the columns and walks the sequence's tokens in order.  A column is shared by LPC neighbouring
+// lanes, each holding RT consecutive rows of it in registers; a sum over the rows ends with log2(LPC) shuffles.
+// Tokens are taken TC at a time through shared memory (coalesced loads, converted to float once; the next TC
+// tokens' loads are in flight, in registers, while the steps run).  For the matrix memory the first column group
+// of every warp carries n instead of a column of S (the same recurrence with v = 1), so that n . q is one
+// shuffle away and no step needs a barrier; the first warp works out the gates of the TC tokens, each lane
+// walking m from the value the block carries, in token order, so that m never depends on where a portion was cut.
+#include "common.cuh"
+
+using namespace vapi;
+
+constexpr int LM_THREADS = 128;
+constexpr int LM_MLSTM = 0, LM_GLA = 1;
+
+__device__ __forceinline__ float lm_logsigmoid(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
+
+template <int LPC>
+__device__ __forceinline__ float lm_lanes_sum(float v) {
+#pragma unroll
+    for (int o = LPC >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+template <typename T, int RT, int LPC, int MODE>
+struct LmShape {
+    static constexpr int RP = RT * LPC;                        // rows, padded to what the lanes hold
+    static constexpr int LANE = RT + 4;                        // floats from one lane's rows to the next lane's
+    static constexpr int RPP = LANE * LPC;                     // a row vector in shared memory
+    static constexpr int TC = RP > 128 ? 8 : 16;               // tokens a round
+    static constexpr int G = 32 / LPC;                         // column groups a warp
+    static constexpr int WARPS = LM_THREADS / 32;
+    static constexpr int CW = MODE == LM_MLSTM ? G - 1 : G;    // columns of S a warp
+    static constexpr int CB = CW * WARPS;                      // columns of S a block
+    static constexpr int NV = MODE == LM_GLA ? 3 : 2;          // row vectors a token: k, q (, decay)
+    static constexpr int NPT = TC * RP / LM_THREADS;           // row elements per thread and vector
+    static constexpr int VPT = (TC * CB + LM_THREADS - 1) / LM_THREADS;
+    static_assert(RT % 4 == 0 && (TC * RP) % LM_THREADS == 0, "rows per lane come in fours");
+    static __device__ __forceinline__ int pad(int r) { return r + (r / RT) * 4; }
+};
+
+template <typename T, int RT, int LPC, int MODE>
+__global__ void __launch_bounds__(LM_THREADS)
+linear_memory_kernel(const T* __restrict__ qkv, long long qkv_stride, int q_off, int k_off, int v_off,
+                     const float* __restrict__ gates, long long gates_stride, const float* __restrict__ gate_bias,
+                     float gate_param, float q_scale, float floor_eps, float* __restrict__ state, long long slot_stride,
+                     const int* __restrict__ state_slots, const int* __restrict__ cu_q, const int* __restrict__ positions,
+                     float* __restrict__ out, int nh, int rows, int cols, int num_slots, int* __restrict__ status) {
+    using Sh = LmShape<T, RT, LPC, MODE>;
+    constexpr int TC = Sh::TC, RPP = Sh::RPP, RP = Sh::RP, CB = Sh::CB, NPT = Sh::NPT, VPT = Sh::VPT;
+    __shared__ __align__(16) float sk[TC * RPP], sq[TC * RPP];
+    __shared__ __align__(16) float sa[MODE == LM_GLA ? TC * RPP : 4];
+    __shared__ float sv[TC * CB];
+    __shared__ float s_keep[TC], s_take[TC], s_floor[TC], s_li[TC], s_lf[TC];
+    const int s = blockIdx.z, h = blockIdx.y;
+    const int col0 = blockIdx.x * CB;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int grp = lane / LPC, sl = lane % LPC;
+    const bool is_n = MODE == LM_MLSTM && grp == 0;
+    const int lc = MODE == LM_MLSTM ? warp * Sh::CW + grp - 1 : warp * Sh::CW + grp;     // column within the block
+    const int col = col0 + lc;
+    const bool col_ok = !is_n && col < cols;
+    const int r0 = sl * RT;
+    const int t0 = cu_q[s], qlen = cu_q[s + 1] - t0;
+    if (qlen <= 0) return;
+    const int slot = state_slots[s];
+    if (slot < 0 || slot >= num_slots) {
+        if (threadIdx.x == 0 && status) atomicExch(status, 3);
+        return;
+    }
+    float* S_glob = state + (size_t)slot * slot_stride + ((size_t)h * rows) * cols;
+    float* n_glob = state + (size_t)slot * slot_stride + (size_t)nh * rows * cols + (size_t)h * rows;
+    float* m_glob = state + (size_t)slot * slot_stride + (size_t)nh * rows * cols + (size_t)nh * rows + h;
+    const bool fresh = positions[t0] == 0;
+    const float bias_i = (MODE == LM_MLSTM && gate_bias) ? gate_bias[h] : 0.f;
+    const float bias_f = (MODE == LM_MLSTM && gate_bias) ? gate_bias[nh + h] : 0.f;
+    pdl_wait();
+    float S[RT];
+#pragma unroll
+    for (int j = 0; j < RT; ++j) {
+        S[j] = 0.f;
+        if (!fresh && r0 + j < rows) {
+            if (is_n) S[j] = n_glob[r0 + j];
+            else if (col_ok) S[j] = S_glob[(size_t)(r0 + j) * cols + col];
+        }
+    }
+    float m_run = (MODE == LM_MLSTM && !fresh) ? *m_glob : 0.f;          // (every lane of the first warp carries it)
+
+    // the next round's inputs, in registers
+    T ra[NPT], rb[NPT], rv[VPT];
+    float rz[MODE == LM_GLA ? NPT : 1];
+    float g_i = 0.f, g_f = 0.f;
+    auto fetch = [&](int first) {
+        const int count = min(TC, qlen - first);
+#pragma unroll
+        for (int e = 0; e < NPT; ++e) {
+            const int idx = threadIdx.x + e * LM_THREADS;
+            const int tt = idx / RP, r = idx - tt * RP;
+            const bool ok = tt < count && r < rows;
+            const T* row = qkv + (size_t)(t0 + first + tt) * qkv_stride;
+            ra[e] = ok ? row[k_off + h * rows + r] : from_f32<T>(0.f);
+            rb[e] = ok ? row[q_off + h * rows + r] : from_f32<T>(0.f);
+            if (MODE == LM_GLA) rz[e] = ok ? gates[(size_t)(t0 + first + tt) * gates_stride + h * rows + r] : 0.f;
+        }
+#pragma unroll
+        for (int e = 0; e < VPT; ++e) {
+            const int idx = threadIdx.x + e * LM_THREADS;
+            const int tt = idx / CB, c = idx - tt * CB;
+            const bool ok = idx < TC * CB && tt < count && col0 + c < cols;
+            rv[e] = ok ? qkv[(size_t)(t0 + first + tt) * qkv_stride + v_off + h * cols + col0 + c] : from_f32<T>(0.f);
+        }
+        if (MODE == LM_MLSTM && (int)threadIdx.x < count) {
+            g_i = gates[(size_t)(t0 + first + threadIdx.x) * gates_stride + h];
+            g_f = gates[(size_t)(t0 + first + threadIdx.x) * gates_stride + nh + h];
+        }
+    };
+    fetch(0);
+    for (int first = 0; first < qlen; first += TC) {
+        const int count = min(TC, qlen - first);
+        __syncthreads();                                    // the steps of the last round have read shared memory
+#pragma unroll
+        for (int e = 0; e < NPT; ++e) {
+            const int idx = threadIdx.x + e * LM_THREADS;
+            const int tt = idx / RP, r = idx - tt * RP;
+            sk[tt * RPP + Sh::pad(r)] = to_f32(ra[e]);
+            sq[tt * RPP + Sh::pad(r)] = to_f32(rb[e]) * q_scale;
+            if (MODE == LM_GLA) sa[tt * RPP + Sh::pad(r)] = expf(lm_logsigmoid(rz[e]) * gate_param);
+        }
+#pragma unroll
+        for (int e = 0; e < VPT; ++e)
+            if (threadIdx.x + e * LM_THREADS < TC * CB) sv[threadIdx.x + e * LM_THREADS] = to_f32(rv[e]);
+        if (MODE == LM_MLSTM && warp == 0) {
+            if (lane < count) {
+                s_li[lane] = gate_param * tanhf((g_i + bias_i) / gate_param);
+                s_lf[lane] = lm_logsigmoid(gate_param * tanhf((g_f + bias_f) / gate_param));
+            }
+            __syncwarp();
+            // lane t walks m over the round's tokens 0 .. t, as the recurrence does, and keeps its own token's factors
+            float m = m_run, m_before = m_run;
+            for (int u = 0; u <= min(lane, count - 1); ++u) {
+                m_before = m;
+                m = fmaxf(s_lf[u] + m, s_li[u]);
+            }
+            if (lane < count) {
+                s_keep[lane] = expf(s_lf[lane] + m_before - m);
+                s_take[lane] = expf(s_li[lane] - m);
+                s_floor[lane] = expf(-m);
+            }
+            m_run = __shfl_sync(0xffffffffu, m, count - 1);
+        }
+        __syncthreads();
+        if (first + TC < qlen) fetch(first + TC);           // in flight while these steps run
+#pragma unroll 2
+        for (int tt = 0; tt < count; ++tt) {
+            const float4* k4 = reinterpret_cast<const float4*>(sk + tt * RPP + sl * Sh::LANE);
+            const float4* q4 = reinterpret_cast<const float4*>(sq + tt * RPP + sl * Sh::LANE);
+            const float4* a4 = reinterpret_cast<const float4*>(sa + (MODE == LM_GLA ? tt * RPP + sl * Sh::LANE : 0));
+            const float vv = is_n ? 1.f : sv[tt * CB + (lc < CB ? lc : 0)];
+            float dot0 = 0.f, dot1 = 0.f;
+            if (MODE == LM_MLSTM) {
+                const float keep = s_keep[tt], tv = s_take[tt] * vv;
+#pragma unroll
+                for (int r4 = 0; r4 < RT / 4; ++r4) {
+                    const float4 kv = k4[r4], qv = q4[r4];
+                    S[4 * r4] = fmaf(kv.x, tv, keep * S[4 * r4]);
+                    S[4 * r4 + 1] = fmaf(kv.y, tv, keep * S[4 * r4 + 1]);
+                    S[4 * r4 + 2] = fmaf(kv.z, tv, keep * S[4 * r4 + 2]);
+                    S[4 * r4 + 3] = fmaf(kv.w, tv, keep * S[4 * r4 + 3]);
+                    dot0 = fmaf(S[4 * r4], qv.x, dot0);
+                    dot1 = fmaf(S[4 * r4 + 1], qv.y, dot1);
+                    dot0 = fmaf(S[4 * r4 + 2], qv.z, dot0);
+                    dot1 = fmaf(S[4 * r4 + 3], qv.w, dot1);
+                }
+            } else {
+#pragma unroll
+                for (int r4 = 0; r4 < RT / 4; ++r4) {
+                    const float4 kv = k4[r4], qv = q4[r4], av = a4[r4];
+                    S[4 * r4] = fmaf(kv.x, vv, av.x * S[4 * r4]);
+                    S[4 * r4 + 1] = fmaf(kv.y, vv, av.y * S[4 * r4 + 1]);
+                    S[4 * r4 + 2] = fmaf(kv.z, vv, av.z * S[4 * r4 + 2]);
+                    S[4 * r4 + 3] = fmaf(kv.w, vv, av.w * S[4 * r4 + 3]);
+                    dot0 = fmaf(S[4 * r4], qv.x, dot0);
+                    dot1 = fmaf(S[4 * r4 + 1], qv.y, dot1);
+                    dot0 = fmaf(S[4 * r4 + 2], qv.z, dot0);
+                    dot1 = fmaf(S[4 * r4 + 3], qv.w, dot1);
+                }
+            }
+            float o = lm_lanes_sum<LPC>(dot0 + dot1);
+            if (MODE == LM_MLSTM) {
+                const float nq = __shfl_sync(0xffffffffu, o, 0);         // the first group's sum is n . q
+                o = o / (fmaxf(fabsf(nq), s_floor[tt]) + floor_eps);
+            }
+            if (sl == 0 && col_ok) out[((size_t)(t0 + first + tt) * nh + h) * cols + col] = o;
+        }
+    }
+    pdl_trigger();                                          // (the next kernel is let go when the walk is over)
+#pragma unroll
+    for (int j = 0; j < RT; ++j) {
+        if (r0 + j >= rows) continue;
+        if (is_n) {
+            if (blockIdx.x == 0 && warp == 0) n_glob[r0 + j] = S[j];
+        } else if (col_ok) {
+            S_glob[(size_t)(r0 + j) * cols + col] = S[j];
+        }
+    }
+    if (MODE == LM_MLSTM && blockIdx.x == 0 && threadIdx.x == 0) *m_glob = m_run;
+}
+
+// (RT, LPC) by the number of rows: 8 x 4 up to 32, 16 x 8 up to 128, 16 x 16 up to 256
+#define LM_DISPATCH(ROWS, CALL)                                     \
+    do {                                                            \
+        if ((ROWS) <= 32) { CALL(8, 4); }                           \
+        else if ((ROWS) <= 128) { CALL(16, 8); }                    \
+        else { CALL(16, 16); }                                      \
+    } while (0)
+
+static inline int lm_lpc(int rows) { return rows <= 32 ? 4 : (rows <= 128 ? 8 : 16); }
+
+static int lm_launch(int mode, const void* qkv, long long qkv_stride, int q_off, int k_off, int v_off, int dtype,
+                     const float* gates, long long gates_stride, const float* gate_bias, float gate_param, float q_scale,
+                     float floor_eps, float* state, long long slot_stride, const int* state_slots, const int* cu_q,
+                     const int* positions, float* out, int num_seqs, int nh, int rows, int cols, int num_slots, int max_q,
+                     int* status, cudaStream_t stream, const char* what) {
+    if (num_seqs <= 0) return 0;
+    if (nh <= 0 || rows <= 0 || rows > 256 || cols <= 0)
+        return fail(-1, "%s: %d heads, state %d x %d (rows up to 256)", what, nh, rows, cols);
+    if (dtype != VAPI_F32 && dtype != VAPI_BF16) return fail(-2, "%s: unsupported dtype %d", what, dtype);
+    const int g = 32 / lm_lpc(rows);
+    const int cb = (mode == LM_MLSTM ? g - 1 : g) * (LM_THREADS / 32);
+    dim3 grid((cols + cb - 1) / cb, nh, num_seqs);
+    if (grid.y > 65535 || grid.z > 65535) return fail(-1, "%s: %d heads x %d sequences are too many", what, nh, num_seqs);
+    const bool early = max_q < 16;                         // decode steps may start beside the kernel before; long walks may not
+    cudaError_t e = cudaSuccess;
+#define LM_CALL_MODE(RT, LPC, M)                                                                                           \
+    if (dtype == VAPI_F32)                                                                                                 \
+        e = launch_if(early, linear_memory_kernel<float, RT, LPC, M>, grid, LM_THREADS, 0, stream, (const float*)qkv,      \
+                      qkv_stride, q_off, k_off, v_off, gates, gates_stride, gate_bias, gate_param, q_scale, floor_eps,     \
+                      state, slot_stride, state_slots, cu_q, positions, out, nh, rows, cols, num_slots, status);           \
+    else                                                                                                                   \
+        e = launch_if(early, linear_memory_kernel<__nv_bfloat16, RT, LPC, M>, grid, LM_THREADS, 0, stream,                 \
+                      (const __nv_bfloat16*)qkv, qkv_stride, q_off, k_off, v_off, gates, gates_stride, gate_bias,          \
+                      gate_param, q_scale, floor_eps, state, slot_stride, state_slots, cu_q, positions, out, nh, rows,     \
+                      cols, num_slots, status)
+#define LM_CALL_A(RT, LPC) LM_CALL_MODE(RT, LPC, LM_MLSTM)
+#define LM_CALL_B(RT, LPC) LM_CALL_MODE(RT, LPC, LM_GLA)
+    if (mode == LM_MLSTM) LM_DISPATCH(rows, LM_CALL_A);
+    else LM_DISPATCH(rows, LM_CALL_B);
+#undef LM_CALL_A
+#undef LM_CALL_B
+#undef LM_CALL_MODE
+    return check_launch(what, e);
+}
+
+// qkv [n, *]: q heads [nh, rows] at q_off, k heads [nh, rows] at k_off, v heads [nh, cols] at v_off of a row of
+// `qkv_stride` elements.  gates [n, *] float: the input gates' pre-activations [nh], then the forget gates' [nh];
+// gate_bias [2 * nh] likewise (may be null).  state: S [nh, rows, cols], n [nh, rows], m [nh] per slot.  out [n, nh * cols] float.
+VAPI_EXPORT int vapi_matrix_memory(const void* qkv, long long qkv_stride, int q_off, int k_off, int v_off, int dtype,
+                                   const float* gates, long long gates_stride, const float* gate_bias, float cap,
+                                   float q_scale, float floor_eps, float* state, long long slot_stride,
+                                   const int* state_slots, const int* cu_q, const int* positions, float* out, int num_seqs,
+                                   int nh, int rows, int cols, int num_slots, int max_q, int* status, cudaStream_t stream) {
+    if (!(cap > 0.f)) return fail(-1, "matrix_memory: the gates' cap must be positive");
+    return lm_launch(LM_MLSTM, qkv, qkv_stride, q_off, k_off, v_off, dtype, gates, gates_stride, gate_bias, cap, q_scale,
+                     floor_eps, state, slot_stride, state_slots, cu_q, positions, out, num_seqs, nh, rows, cols, num_slots,
+                     max_q, status, stream, "matrix_memory");
+}
+
+// As above without gates' scalars: decay_logits [n, *] float holds z [nh, rows] per token; alpha = sigmoid(z)^inv_tau.
+// state: S [nh, rows, cols] per slot.
+VAPI_EXPORT int vapi_gated_linear_attention(const void* qkv, long long qkv_stride, int q_off, int k_off, int v_off, int dtype,
+                                            const float* decay_logits, long long decay_stride, float inv_tau, float q_scale,
+                                            float* state, long long slot_stride, const int* state_slots, const int* cu_q,
+                                            const int* positions, float* out, int num_seqs, int nh, int rows, int cols,
+                                            int num_slots, int max_q, int* status, cudaStream_t stream) {
+    return lm_launch(LM_GLA, qkv, qkv_stride, q_off, k_off, v_off, dtype, decay_logits, decay_stride, nullptr, inv_tau,
+                     q_scale, 0.f, state, slot_stride, state_slots, cu_q, positions, out, num_seqs, nh, rows, cols,
+                     num_slots, max_q, status, stream, "gated_linear_attention");
+}
+
+VAPI_EXPORT const char* vapi_last_error() { return error_buffer(); }

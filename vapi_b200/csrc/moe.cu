@@ -7,12 +7,15 @@
 // can be chosen (the others count as minus infinity); the `top` largest choice scores win (ties: the
 // lower index); their weights are their s divided by the sum of the chosen s (+ 1e-20).  An output
 // index >= experts is an identity expert: its output is the input itself.
+// A second way of scoring (score_mode 1): the choice is made among the logits z = Wr h + bias themselves, and the
+// weights are the softmax over the chosen logits only.
 //
 // The step's expert work is laid out without the host learning anything about it: after the router, one
 // block counts the (token, choice) pairs of each expert in shared memory (a pair's rank within its expert is
 // the count it met), turns the counts into offsets, lists the pairs expert by expert and cuts each expert's
 // list into tiles of 64 rows.  The two products launch enough blocks for the worst case; a block whose tile does
-// not exist returns at once.  up: hid[pos] = relu(W_up[e] h[token])^2; down: y[pair] = weight *
+// not exist returns at once.  up: hid[pos] = relu(W_up[e] h[token])^2, or, for experts with a gate,
+// hid[pos] = silu(W_gate[e] h) * (W_up[e] h) from one matrix whose rows alternate gate, up; down: y[pair] = weight *
 // W_down[e] hid[pos] in float; the sum over a token's pairs, its identity experts and the shared expert
 // is taken in a fixed order.
 #include "common.cuh"
@@ -47,6 +50,7 @@ template <> struct RtLd4<__nv_bfloat16> {
 template <typename T>
 __global__ void __launch_bounds__(128)
 moe_route_kernel(const T* __restrict__ h, const float* __restrict__ wr, const float* __restrict__ corr,
+                 const float* __restrict__ bias, int score_mode,
                  int* __restrict__ ids, float* __restrict__ wts, int n, int width, int outputs, int experts, int top,
                  int groups, int keep, int vec4) {
     extern __shared__ float rt_smem[];
@@ -87,7 +91,7 @@ moe_route_kernel(const T* __restrict__ h, const float* __restrict__ wr, const fl
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const float v = warp_sum(acc[j]);
-            if (lane == 0 && e0 + j < outputs) s[e0 + j] = v;
+            if (lane == 0 && e0 + j < outputs) s[e0 + j] = bias ? v + bias[e0 + j] : v;
         }
     }
     __syncthreads();
@@ -95,6 +99,9 @@ moe_route_kernel(const T* __restrict__ h, const float* __restrict__ wr, const fl
     {
 
     __syncwarp();
+    if (score_mode == 1) {
+        for (int e = lane; e < outputs; e += 32) choice[e] = s[e];
+    } else {
     float mx = -INFINITY;
     for (int e = lane; e < outputs; e += 32) mx = fmaxf(mx, s[e]);
     mx = warp_max(mx);
@@ -104,7 +111,8 @@ moe_route_kernel(const T* __restrict__ h, const float* __restrict__ wr, const fl
     for (int e = lane; e < outputs; e += 32) {
         const float p = expf(s[e] - mx) / sum;
         s[e] = p;
-        choice[e] = p + corr[e];
+        choice[e] = p + (corr ? corr[e] : 0.f);
+    }
     }
     __syncwarp();
     if (groups > 1 && keep < groups) {
@@ -160,7 +168,18 @@ moe_route_kernel(const T* __restrict__ h, const float* __restrict__ wr, const fl
         }
         __syncwarp();
     }
-    if (lane == 0) {
+    if (lane == 0 && score_mode == 1) {
+        // the softmax over the chosen logits; the first choice is the largest
+        const float z0 = wts[(size_t)t * top];
+        float sum = 0.f;
+        for (int r = 0; r < top; ++r) {
+            const float p = expf(wts[(size_t)t * top + r] - z0);
+            wts[(size_t)t * top + r] = p;
+            sum += p;
+        }
+        const float inv = 1.f / sum;
+        for (int r = 0; r < top; ++r) wts[(size_t)t * top + r] *= inv;
+    } else if (lane == 0) {
         const float inv = 1.f / (total + 1e-20f);
         for (int r = 0; r < top; ++r) wts[(size_t)t * top + r] *= inv;
     }
@@ -211,7 +230,8 @@ __global__ void moe_plan_kernel(const int* __restrict__ ids, int* __restrict__ r
 
 // out rows of one tile = act(A rows x W[e]^T): A [*, K] rows gathered through `src` (pair / src_div when
 // gather, else the sorted position itself), W [experts, N, K].  MODE 0 (up): out[pos, :] = relu(.)^2 in T.
-// MODE 1 (down): out[pair, :] = weight[pair] * (.) in float.
+// MODE 1 (down): out[pair, :] = weight[pair] * (.) in float.  MODE 2 (gate and up in one matrix, rows alternating
+// gate_j, up_j): out[pos, j] = silu(gate_j) * up_j in T, out having N / 2 columns.
 template <typename T, int MODE>
 __global__ void __launch_bounds__(256)
 moe_grouped_kernel(const T* __restrict__ A, long long a_stride, const T* __restrict__ W, const int* __restrict__ plan,
@@ -234,8 +254,8 @@ moe_grouped_kernel(const T* __restrict__ A, long long a_stride, const T* __restr
         if ((int)threadIdx.x < rows) {
             const int pos = row0 + threadIdx.x;
             const int pair = pair_of[pos];
-            src = MODE == 0 ? pair / top : pos;
-            dst = MODE == 0 ? pos : pair;
+            src = MODE != 1 ? pair / top : pos;
+            dst = MODE != 1 ? pos : pair;
         }
         s_src[threadIdx.x] = src;
         s_dst[threadIdx.x] = dst;
@@ -277,15 +297,25 @@ moe_grouped_kernel(const T* __restrict__ A, long long a_stride, const T* __restr
         const int dst = s_dst[ty * 4 + i];
         if (dst < 0) continue;
         const float g = MODE == 1 ? wts[dst] : 1.f;
+        if (MODE == 2) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const int c = c0 + tx * 4 + j;
-            if (c >= N) continue;
-            if (MODE == 0) {
-                const float r = fmaxf(acc[i][j], 0.f);
-                reinterpret_cast<T*>(out)[(size_t)dst * N + c] = from_f32<T>(r * r);
-            } else {
-                reinterpret_cast<float*>(out)[(size_t)dst * N + c] = g * acc[i][j];
+            for (int j = 0; j < 4; j += 2) {
+                const int c = c0 + tx * 4 + j;
+                if (c + 1 >= N) continue;
+                const float gv = acc[i][j], uv = acc[i][j + 1];
+                reinterpret_cast<T*>(out)[(size_t)dst * (N >> 1) + (c >> 1)] = from_f32<T>(gv / (1.f + expf(-gv)) * uv);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int c = c0 + tx * 4 + j;
+                if (c >= N) continue;
+                if (MODE == 0) {
+                    const float r = fmaxf(acc[i][j], 0.f);
+                    reinterpret_cast<T*>(out)[(size_t)dst * N + c] = from_f32<T>(r * r);
+                } else {
+                    reinterpret_cast<float*>(out)[(size_t)dst * N + c] = g * acc[i][j];
+                }
             }
         }
     }
@@ -318,8 +348,8 @@ moe_grouped_mma_kernel(const __nv_bfloat16* __restrict__ A, long long a_stride, 
         if (r < rows) {
             const int pos = row0 + r;
             const int pair = pair_of[pos];
-            ap = A + (size_t)(MODE == 0 ? pair / top : pos) * a_stride;
-            dst = MODE == 0 ? pos : pair;
+            ap = A + (size_t)(MODE != 1 ? pair / top : pos) * a_stride;
+            dst = MODE != 1 ? pos : pair;
         }
         a_rows[r] = ap;
         s_dst[r] = dst;
@@ -340,7 +370,12 @@ moe_grouped_mma_kernel(const __nv_bfloat16* __restrict__ A, long long a_stride, 
             for (int ni = 0; ni < Tile::NI; ++ni) {
                 const int c = c0 + wn * (BN / WN) + ni * 8 + 2 * t;
                 const float v0 = acc[mi][ni][2 * h], v1 = acc[mi][ni][2 * h + 1];
-                if (MODE == 0) {
+                if (MODE == 2) {
+                    // (c is even: v0 is a gate's row, v1 the up row that belongs to it)
+                    if (c + 1 < N)
+                        reinterpret_cast<__nv_bfloat16*>(out)[(size_t)dst * (N >> 1) + (c >> 1)] =
+                            __float2bfloat16_rn(v0 / (1.f + expf(-v0)) * v1);
+                } else if (MODE == 0) {
                     const float r0 = fmaxf(v0, 0.f), r1 = fmaxf(v1, 0.f);
                     __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)dst * N + c;
                     if (c + 1 < N && (N & 1) == 0) *reinterpret_cast<__nv_bfloat162*>(o) = __floats2bfloat162_rn(r0 * r0, r1 * r1);
@@ -425,7 +460,8 @@ VAPI_EXPORT int vapi_relu_squared(const void* x, void* out, int dtype, long long
 
 // ids, wts, ranks: [n, top]; offsets: [experts + 1]; pair_of: [n * top];
 // plan: [1]; tile_expert, tile_row0: [max_tiles] with max_tiles >= n * top / 64 + experts.
-VAPI_EXPORT int vapi_moe_route(const void* h, int dtype, const float* wr, const float* corr, int* ids, float* wts, int* ranks,
+VAPI_EXPORT int vapi_moe_route(const void* h, int dtype, const float* wr, const float* corr, const float* bias,
+                               int score_mode, int* ids, float* wts, int* ranks,
                                int* offsets, int* pair_of, int* plan, int* tile_expert, int* tile_row0, int n,
                                int width, int outputs, int experts, int top, int groups, int keep, cudaStream_t stream) {
     if (n <= 0) return 0;
@@ -439,11 +475,11 @@ VAPI_EXPORT int vapi_moe_route(const void* h, int dtype, const float* wr, const 
     if (smem > 48 * 1024) return fail(-1, "moe_route: %d router outputs are too many", outputs);
     const int vec4 = (width % 4 == 0 && ((uintptr_t)h & 15) == 0 && ((uintptr_t)wr & 15) == 0) ? 1 : 0;
     if (dtype == VAPI_F32)
-        e = launch(moe_route_kernel<float>, n, 128, smem, stream, (const float*)h, wr, corr, ids, wts, n, width, outputs,
-                   experts, top, groups, keep, vec4);
-    else if (dtype == VAPI_BF16)
-        e = launch(moe_route_kernel<__nv_bfloat16>, n, 128, smem, stream, (const __nv_bfloat16*)h, wr, corr, ids, wts, n,
+        e = launch(moe_route_kernel<float>, n, 128, smem, stream, (const float*)h, wr, corr, bias, score_mode, ids, wts, n,
                    width, outputs, experts, top, groups, keep, vec4);
+    else if (dtype == VAPI_BF16)
+        e = launch(moe_route_kernel<__nv_bfloat16>, n, 128, smem, stream, (const __nv_bfloat16*)h, wr, corr, bias, score_mode, ids,
+                   wts, n, width, outputs, experts, top, groups, keep, vec4);
     else
         return fail(-2, "moe_route: unsupported dtype %d", dtype);
     int rc = check_launch("moe_route", e);
@@ -462,6 +498,7 @@ VAPI_EXPORT int vapi_moe_grouped(const void* A, long long a_stride, const void* 
                                  const float* wts, void* out, int pairs, int experts, int N, int K, int top, int mode,
                                  cudaStream_t stream) {
     if (pairs <= 0 || experts <= 0) return 0;
+    if (mode < 0 || mode > 2 || (mode == 2 && (N & 1))) return fail(-1, "moe_grouped: mode %d with %d output rows", mode, N);
     const int max_tiles = pairs / MOE_TM + experts;
     dim3 grid(max_tiles, (N + MOE_TN - 1) / MOE_TN);
     if (grid.y > 65535) return fail(-1, "moe_grouped: %d output features are too many", N);
@@ -482,7 +519,7 @@ VAPI_EXPORT int vapi_moe_grouped(const void* A, long long a_stride, const void* 
         e = launch(kern, g, Tile::THREADS, Tile::SMEM, stream, (const __nv_bfloat16*)A, a_stride, (const __nv_bfloat16*)W,   \
                    plan, tile_expert, tile_row0, offsets, pair_of, wts, out, N, K, top);                                     \
     } while (0)
-        if (mode == 0) MOE_TC(0, 64, 64, 2, 2); else MOE_TC(1, 64, 64, 2, 2);
+        if (mode == 0) MOE_TC(0, 64, 64, 2, 2); else if (mode == 1) MOE_TC(1, 64, 64, 2, 2); else MOE_TC(2, 64, 64, 2, 2);
 #undef MOE_TC
         return check_launch("moe_grouped (tensor cores)", e);
     }
@@ -490,8 +527,10 @@ VAPI_EXPORT int vapi_moe_grouped(const void* A, long long a_stride, const void* 
 #define MOE_GO(T, M)                                                                                                         \
     e = launch(moe_grouped_kernel<T, M>, grid, 256, 0, stream, (const T*)A, a_stride, (const T*)W, plan, tile_expert,         \
                tile_row0, offsets, pair_of, wts, out, N, K, top)
-    if (dtype == VAPI_F32) { if (mode == 0) MOE_GO(float, 0); else MOE_GO(float, 1); }
-    else if (dtype == VAPI_BF16) { if (mode == 0) MOE_GO(__nv_bfloat16, 0); else MOE_GO(__nv_bfloat16, 1); }
+    if (dtype == VAPI_F32) { if (mode == 0) MOE_GO(float, 0); else if (mode == 1) MOE_GO(float, 1); else MOE_GO(float, 2); }
+    else if (dtype == VAPI_BF16) {
+        if (mode == 0) MOE_GO(__nv_bfloat16, 0); else if (mode == 1) MOE_GO(__nv_bfloat16, 1); else MOE_GO(__nv_bfloat16, 2);
+    }
     else return fail(-2, "moe_grouped: unsupported dtype %d", dtype);
 #undef MOE_GO
     return check_launch("moe_grouped", e);

@@ -387,10 +387,99 @@ __global__ void qk_norm_rope_write_split_kernel(T* __restrict__ qkv, long long r
     }
 }
 
+// The same work where the RMS norm of q (and of k) runs over the whole projection of a token, all heads at
+// once, with a weight per element of the projection (qw [nh * dk], kw [nkv * dk]); eps inside the root.  One
+// block per token: every thread adds up its share of the squares of q and of k in a fixed order, the block
+// sums them, and then the warps share out the heads: q is normed (and rotated) in place, k and v go to the
+// page.  The sums depend on the token's row alone, never on what else is in the step.
+template <typename T>
+__global__ void qk_norm_whole_write_split_kernel(T* __restrict__ qkv, long long row_stride, const float* __restrict__ qw,
+                                                 const float* __restrict__ kw, float eps,
+                                                 const float* __restrict__ cosr, const float* __restrict__ sinr,
+                                                 int rot, int interleaved, T* __restrict__ cache,
+                                                 const int* __restrict__ slot_mapping, int n, int nh, int nkv,
+                                                 int dk, int dv, int page_size, int num_pages,
+                                                 int* __restrict__ status) {
+    __shared__ float sh[QK_WARPS][QK_MAX_D];
+    __shared__ float red[33];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x;
+    pdl_trigger();
+    if (t >= n) {
+        pdl_wait();
+        return;
+    }
+    const int slot = cache ? slot_mapping[t] : 0;
+    pdl_wait();
+    T* row = qkv + (size_t)t * row_stride;
+    const int q_len = nh * dk, k_len = nkv * dk;
+    float ssq = 0.f, ssk = 0.f;
+    for (int i = threadIdx.x; i < q_len; i += blockDim.x) {
+        const float v = to_f32(row[i]);
+        ssq = fmaf(v, v, ssq);
+    }
+    for (int i = threadIdx.x; i < k_len; i += blockDim.x) {
+        const float v = to_f32(row[q_len + i]);
+        ssk = fmaf(v, v, ssk);
+    }
+    ssq = block_sum(ssq, red);
+    ssk = block_sum(ssk, red);
+    const float inv_q = qw ? rsqrtf(ssq / (float)q_len + eps) : 1.f;
+    const float inv_k = kw ? rsqrtf(ssk / (float)max(k_len, 1) + eps) : 1.f;
+    int page = 0, off = 0;
+    if (cache) {
+        page = slot / page_size;
+        off = slot - page * page_size;
+        if (slot < 0 || page >= num_pages) {
+            if (threadIdx.x == 0 && status) atomicExch(status, 2);
+            return;
+        }
+    }
+    const int heads = nh + 2 * nkv;
+    const int half = rot >> 1;
+    const size_t page_elems = (size_t)nkv * page_size * (dk + dv);
+    float* s = sh[warp];
+    for (int h = warp; h < heads; h += QK_WARPS) {
+        const bool is_q = h < nh, is_k = !is_q && h < nh + nkv;
+        const int d = (is_q || is_k) ? dk : dv;
+        T* src = row + (is_q || is_k ? (size_t)h * dk : (size_t)(nh + nkv) * dk + (size_t)(h - nh - nkv) * dv);
+        const float* w = is_q ? (qw ? qw + (size_t)h * dk : nullptr) : (is_k && kw ? kw + (size_t)(h - nh) * dk : nullptr);
+        const float inv = is_q ? inv_q : inv_k;
+        const bool rope = (is_q || is_k) && cosr != nullptr;
+        T* dst = nullptr;
+        if (is_q) dst = src;
+        else if (cache)
+            dst = is_k ? cache + (size_t)page * page_elems + ((size_t)(h - nh) * page_size + off) * dk
+                       : cache + (size_t)page * page_elems + (size_t)nkv * page_size * dk + ((size_t)(h - nh - nkv) * page_size + off) * dv;
+        if (!dst) continue;
+        __syncwarp();
+        for (int i = lane; i < d; i += 32) s[i] = to_f32(src[i]);
+        __syncwarp();
+        for (int i = lane; i < d; i += 32) {
+            float v = w ? s[i] * inv * w[i] : s[i];
+            if (rope && i < rot) {
+                int j, pi;
+                bool first;
+                if (interleaved) {
+                    j = i >> 1; first = (i & 1) == 0; pi = i ^ 1;
+                } else {
+                    first = i < half; j = first ? i : i - half; pi = first ? i + half : i - half;
+                }
+                const float pv = w ? s[pi] * inv * w[pi] : s[pi];
+                const float c = cosr[(size_t)t * half + j], sn = sinr[(size_t)t * half + j];
+                v = first ? v * c - pv * sn : v * c + pv * sn;
+            }
+            dst[i] = from_f32<T>(v);
+        }
+    }
+}
+
+
 VAPI_EXPORT int vapi_qk_norm_rope_write_split(void* qkv, long long row_stride, int dtype, const float* qw, const float* kw,
                                               float eps, const float* cosr, const float* sinr, int rot, int interleaved,
                                               void* cache, const int* slot_mapping, int n, int nh, int nkv, int dk,
-                                              int dv, int page_size, int num_pages, int* status, cudaStream_t stream) {
+                                              int dv, int page_size, int num_pages, int whole, int* status,
+                                              cudaStream_t stream) {
     if (n <= 0) return 0;
     if (dk <= 0 || dk > QK_MAX_D || dv <= 0 || dv > QK_MAX_D)
         return fail(-1, "qk_norm_rope_write_split: head sizes %d/%d are outside 1..%d", dk, dv, QK_MAX_D);
@@ -404,6 +493,19 @@ VAPI_EXPORT int vapi_qk_norm_rope_write_split(void* qkv, long long row_stride, i
     const long long items = (long long)n * (nh + 2 * nkv);
     const int blocks = (int)((items + QK_WARPS - 1) / QK_WARPS);
     cudaError_t e;
+    if (whole) {                 // the norms run over a token's whole q and k: a block per token
+        if (dtype == VAPI_F32)
+            e = launch(qk_norm_whole_write_split_kernel<float>, n, QK_WARPS * 32, 0, stream, (float*)qkv, row_stride, qw, kw,
+                       eps, cosr, sinr, rot, interleaved, (float*)cache, slot_mapping, n, nh, nkv, dk, dv, page_size,
+                       num_pages, status);
+        else if (dtype == VAPI_BF16)
+            e = launch(qk_norm_whole_write_split_kernel<__nv_bfloat16>, n, QK_WARPS * 32, 0, stream, (__nv_bfloat16*)qkv,
+                       row_stride, qw, kw, eps, cosr, sinr, rot, interleaved, (__nv_bfloat16*)cache, slot_mapping, n, nh,
+                       nkv, dk, dv, page_size, num_pages, status);
+        else
+            return fail(-2, "qk_norm_rope_write_split: unsupported dtype %d", dtype);
+        return check_launch("qk_norm_rope_write_split (whole projection)", e);
+    }
     if (dtype == VAPI_F32)
         e = launch(qk_norm_rope_write_split_kernel<float>, blocks, QK_WARPS * 32, 0, stream, (float*)qkv, row_stride, qw, kw, eps,
                    cosr, sinr, rot, interleaved, (float*)cache, slot_mapping, n, nh, nkv, dk, dv, page_size, num_pages, status);

@@ -1018,38 +1018,49 @@ def apply_penalties(logits: torch.Tensor, rows: torch.Tensor, toks: torch.Tensor
 # ---------------------------------------------------------------------------------------
 # blocks that norm a sublayer on both sides; rotary tables with scaled frequencies; attention
 # with unlike key and value widths, chunked masks, sinks and head gates; recurrent mixers
-def postnorm_add_rmsnorm(x: torch.Tensor, y: torch.Tensor, post_weight: torch.Tensor, post_eps: float, mult: float,
-                         weight: Optional[torch.Tensor], eps: float, out_dtype: torch.dtype,
-                         rows: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+def postnorm_add_rmsnorm(x: torch.Tensor, y: Optional[torch.Tensor], post_weight: Optional[torch.Tensor], post_eps: float,
+                         mult: float, weight: Optional[torch.Tensor], eps: float, out_dtype: torch.dtype,
+                         rows: Optional[torch.Tensor] = None, copy: bool = False) -> Optional[torch.Tensor]:
     """``x += mult * rmsnorm(y) * post_weight`` on the float32 stream and, with ``weight``,
     ``out = rmsnorm(x) * weight`` in one pass.  With ``rows`` only those rows are produced and
-    ``x`` is left untouched.  ``weight`` None: only the stream is updated (returns None)."""
+    ``x`` is left untouched.  ``y`` None: nothing is pending.  ``weight`` None: no norm follows; with ``copy`` the
+    rows of the stream themselves are returned in ``out_dtype`` (for a sublayer that reads the stream as it is),
+    else only the stream is updated (returns None)."""
     _cuda(x, y, post_weight, weight, rows)
     _f32(x, "residual stream")
     _f32(post_weight, "norm weight")
     _f32(weight, "norm weight")
     _i32(rows, "rows")
-    _contig(y, "sublayer output")
     hidden = x.shape[-1]
-    if y.shape != x.shape or y.dtype != out_dtype:
-        raise KernelError("the sublayer's output must have the stream's shape and the activation dtype")
-    if post_weight.numel() != hidden or (weight is not None and weight.numel() != hidden):
+    if y is not None:
+        _contig(y, "sublayer output")
+        if y.shape != x.shape or y.dtype != out_dtype:
+            raise KernelError("the sublayer's output must have the stream's shape and the activation dtype")
+        if post_weight is None or post_weight.numel() != hidden:
+            raise KernelError(f"norm weights must have {hidden} elements")
+    if weight is not None and weight.numel() != hidden:
         raise KernelError(f"norm weights must have {hidden} elements")
     n_out = rows.numel() if rows is not None else x.shape[0]
-    out = torch.empty((n_out, hidden), dtype=out_dtype, device=x.device) if weight is not None else None
+    wants = weight is not None or copy
+    if y is None and not wants:
+        return None
+    out = torch.empty((n_out, hidden), dtype=out_dtype, device=x.device) if wants else None
     lib = _lib("elementwise")
-    _check(lib, lib.vapi_postnorm_add_rmsnorm(_p(x), _p(y), _dt(y), _p(post_weight), ctypes.c_float(post_eps),
+    _check(lib, lib.vapi_postnorm_add_rmsnorm(_p(x), _p(y), _DT[out_dtype], _p(post_weight), ctypes.c_float(post_eps),
                                               ctypes.c_float(mult), _p(weight), ctypes.c_float(eps), _p(rows), _p(out),
                                               n_out, hidden, _stream()))
     return out
 
 
 def gated_group_rmsnorm(y: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, eps: float, group: int,
-                        gate_first: bool, out_dtype: torch.dtype) -> torch.Tensor:
+                        gate_first: bool, out_dtype: torch.dtype, gate: str = "silu") -> torch.Tensor:
     """RMS norm over equal groups of ``group`` columns of the float32 rows ``y`` [n, width] with a
     SiLU gate ``z`` [n, width] (any row stride): ``norm(y) * weight * silu(z)``, or with
     ``gate_first`` ``norm(y * silu(z)) * weight``.  ``weight`` is indexed by column modulo its
-    length (one weight per group member, or one per column)."""
+    length (one weight per group member, or one per column).  ``gate`` "sigmoid" puts ``sigmoid(z)`` where
+    ``silu(z)`` stands."""
+    if gate not in ("silu", "sigmoid"):
+        raise KernelError(f"gate `{gate}` is not one of silu, sigmoid")
     _cuda(y, z, weight)
     _f32(y, "recurrence output")
     _f32(weight, "norm weight")
@@ -1059,7 +1070,8 @@ def gated_group_rmsnorm(y: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, 
     out = torch.empty((n, width), dtype=out_dtype, device=y.device)
     lib = _lib("elementwise")
     _check(lib, lib.vapi_gated_group_rmsnorm(_p(y), _p(z), ctypes.c_longlong(z.stride(0)), _dt(z), _p(weight),
-                                             weight.numel(), ctypes.c_float(eps), 1 if gate_first else 0, _p(out), n, width,
+                                             weight.numel(), ctypes.c_float(eps),
+                                             (1 if gate_first else 0) | (2 if gate == "sigmoid" else 0), _p(out), n, width,
                                              int(group), _stream()))
     return out
 
@@ -1092,12 +1104,16 @@ def qk_norm_rope_write_split(qkv: torch.Tensor, nh: int, nkv: int, dk: int, dv: 
                              q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
                              cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], rot: int, interleaved: bool,
                              cache_layer: Optional[torch.Tensor], page_size: int, slot_mapping: Optional[torch.Tensor],
-                             status: Optional[torch.Tensor] = None) -> None:
+                             status: Optional[torch.Tensor] = None, whole: bool = False) -> None:
     """:func:`qk_norm_rope_write` for keys of width ``dk`` and values of width ``dv``: ``qkv`` [n, >=
     (nh+nkv)*dk + nkv*dv] holds q heads, k heads, v heads (columns beyond them are left alone);
     the rotation pairs (2i, 2i+1) when ``interleaved``, else (i, i + rot/2); ``cache_layer`` is the
     call site's pages, flat [pages, page_size * nkv * (dk + dv)]: keys [nkv, page_size, dk], then
-    values [nkv, page_size, dv]."""
+    values [nkv, page_size, dv].  ``whole``: the RMS norms run over a token's whole q (and whole k), all heads at
+    once, with weights of ``nh * dk`` and ``nkv * dk`` elements, instead of per head with weights of ``dk``."""
+    for wt, heads, what in ((q_weight, nh, "q"), (k_weight, nkv, "k")):
+        if wt is not None and wt.numel() != (heads * dk if whole else dk):
+            raise KernelError(f"the {what} norm's weight has {wt.numel()} elements")
     _cuda(qkv, q_weight, k_weight, cos, sin, cache_layer, slot_mapping)
     _contig(qkv, "qkv")
     _f32(q_weight, "q norm weight")
@@ -1119,7 +1135,7 @@ def qk_norm_rope_write_split(qkv: torch.Tensor, nh: int, nkv: int, dk: int, dv: 
     _check(lib, lib.vapi_qk_norm_rope_write_split(
         _p(qkv), ctypes.c_longlong(qkv.stride(0)), _dt(qkv), _p(q_weight), _p(k_weight), ctypes.c_float(eps), _p(cos),
         _p(sin), int(rot), 1 if interleaved else 0, _p(cache_layer), _p(slot_mapping), n, nh, nkv, dk, dv, int(page_size),
-        num_pages, _p(status), _stream()))
+        num_pages, 1 if whole else 0, _p(status), _stream()))
 
 
 def masked_attention_splits(num_seqs: int, max_q: int, max_k: int, nh: int, nkv: int) -> int:
@@ -1297,11 +1313,17 @@ def state_space(xbc: torch.Tensor, dt: torch.Tensor, A_log: torch.Tensor, dt_bia
 # ---------------------------------------------------------------------------------------
 # several residual streams, mixers side by side, the gated linear recurrence, a mixture of experts
 def embed_sinusoid(table: torch.Tensor, tokens: torch.Tensor, positions: torch.Tensor, freq: Optional[torch.Tensor],
-                   streams: int = 1, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+                   streams: int = 1, status: Optional[torch.Tensor] = None,
+                   pos_table: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Rows of ``table`` [V, H] for ``tokens`` [n] plus a sinusoidal position vector (entry 2i the sine, entry
     2i+1 the cosine of ``position * freq[i]``; ``freq`` None: nothing is added), as ``streams`` equal copies of
-    the float32 residual stream: [n, streams, H]."""
-    _cuda(table, tokens, positions, freq)
+    the float32 residual stream: [n, streams, H].  ``pos_table`` [P, H] of the table's dtype: row ``position`` of it
+    is added too, as it is (a learned position vector)."""
+    _cuda(table, tokens, positions, freq, pos_table)
+    if pos_table is not None:
+        _contig(pos_table, "position table")
+        if pos_table.dtype != table.dtype or pos_table.dim() != 2 or pos_table.shape[1] != table.shape[1]:
+            raise KernelError("the position table must be [positions, H] of the embedding table's dtype")
     _contig(table, "embedding table")
     _i32(tokens, "tokens")
     _i32(positions, "positions")
@@ -1311,7 +1333,8 @@ def embed_sinusoid(table: torch.Tensor, tokens: torch.Tensor, positions: torch.T
         raise KernelError(f"{freq.numel()} frequencies for rows of {hidden}")
     out = torch.empty((n, int(streams), hidden), dtype=torch.float32, device=table.device)
     lib = _lib("hyper")
-    _check(lib, lib.vapi_embed_sinusoid(_p(table), _dt(table), _p(tokens), _p(positions), _p(freq), _p(out), n, hidden,
+    _check(lib, lib.vapi_embed_sinusoid(_p(table), _dt(table), _p(tokens), _p(positions), _p(freq), _p(pos_table),
+                                        0 if pos_table is None else pos_table.shape[0], _p(out), n, hidden,
                                         vocab, int(streams), _p(status), _stream()))
     return out
 
@@ -1468,22 +1491,28 @@ def relu_squared(x: torch.Tensor) -> torch.Tensor:
     return out
 
 
-def moe_route(h: torch.Tensor, router: torch.Tensor, correction: torch.Tensor, experts: int, top: int, groups: int,
-              keep: int):
+def moe_route(h: torch.Tensor, router: torch.Tensor, correction: Optional[torch.Tensor], experts: int, top: int, groups: int,
+              keep: int, bias: Optional[torch.Tensor] = None, score: str = "softmax"):
     """The router of a mixture of experts for ``h`` [n, W]: ``router`` [outputs, W] and ``correction`` [outputs]
     float32, ``outputs`` = ``experts`` + identity experts.  Scores are the softmax of the float32 logits over all
     outputs; the ``top`` largest of score + correction win, among the outputs of the ``keep`` best of ``groups``
     equal groups of neighbours (a group's score is its largest score + correction); the weights are the chosen
     scores divided by their sum (+ 1e-20).  Returns ``(ids [n, top] int32, weights [n, top] float32, plan)``;
-    ``plan`` lists the step's (token, choice) pairs expert by expert for :func:`moe_experts`."""
-    _cuda(h, router, correction)
+    ``plan`` lists the step's (token, choice) pairs expert by expert for :func:`moe_experts`.  ``bias`` [outputs] is
+    added to the logits.  ``score`` "chosen": the ``top`` largest logits win and the weights are the softmax over
+    the chosen logits only (no correction)."""
+    _cuda(h, router, correction, bias)
+    _f32(bias, "router bias")
+    if score not in ("softmax", "chosen"):
+        raise KernelError(f"score `{score}` is not one of softmax, chosen")
     _contig(h, "router input")
     _f32(router, "router matrix")
     _f32(correction, "router correction")
     n, W = h.shape
     outputs = router.shape[0]
-    if router.shape != (outputs, W) or correction.numel() != outputs:
-        raise KernelError("the router must be [outputs, W] and the correction [outputs]")
+    if router.shape != (outputs, W) or (correction is not None and correction.numel() != outputs) or \
+            (bias is not None and bias.numel() != outputs):
+        raise KernelError("the router must be [outputs, W], the correction and the bias [outputs]")
     dev = h.device
     pairs = n * top
     ids = torch.empty((n, top), dtype=torch.int32, device=dev)
@@ -1498,18 +1527,20 @@ def moe_route(h: torch.Tensor, router: torch.Tensor, correction: torch.Tensor, e
         at += z
     ranks, offsets, pair_of, ntiles, tile_expert, tile_row0 = parts
     lib = _lib("moe")
-    _check(lib, lib.vapi_moe_route(_p(h), _dt(h), _p(router), _p(correction), _p(ids), _p(wts), _p(ranks),
+    _check(lib, lib.vapi_moe_route(_p(h), _dt(h), _p(router), _p(correction), _p(bias), 1 if score == "chosen" else 0,
+                                   _p(ids), _p(wts), _p(ranks),
                                    _p(offsets), _p(pair_of), _p(ntiles), _p(tile_expert), _p(tile_row0), n, W, outputs,
                                    int(experts), int(top), int(groups), int(keep), _stream()), 2 if experts > 0 else 1)
     return ids, wts, (offsets, pair_of, ntiles, tile_expert, tile_row0)
 
 
 def moe_experts(h: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, plan, w_up: Optional[torch.Tensor],
-                w_down: Optional[torch.Tensor], shared: Optional[torch.Tensor] = None) -> torch.Tensor:
+                w_down: Optional[torch.Tensor], shared: Optional[torch.Tensor] = None, gated: bool = False) -> torch.Tensor:
     """The weighted sum of the chosen experts' outputs for ``h`` [n, W]: expert e is ``W_down[e] relu(W_up[e] h)^2``
     with ``w_up`` [experts, ff, W] and ``w_down`` [experts, W, ff] of h's dtype; a choice >= experts is an identity
     expert (its output is h); ``shared`` [n, W] is added when given.  ``ids``, ``wts``, ``plan``: from
-    :func:`moe_route`."""
+    :func:`moe_route`.  ``gated``: expert e is ``W_down[e] (silu(W_gate[e] h) * (W_up[e] h))`` and ``w_up`` is
+    [experts, 2 * ff, W] with rows alternating gate_0, up_0, gate_1, up_1, ..."""
     _cuda(h, ids, wts, w_up, w_down, shared)
     _contig(h, "expert input")
     n, W = h.shape
@@ -1519,17 +1550,18 @@ def moe_experts(h: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, plan, w_u
     y = None
     lib = _lib("moe")
     if experts > 0:
-        ff = w_up.shape[1]
+        rows_up = w_up.shape[1]
+        ff = rows_up // 2 if gated else rows_up
         _contig(w_up, "expert up matrices")
         _contig(w_down, "expert down matrices")
-        if w_up.shape != (experts, ff, W) or w_down.shape != (experts, W, ff) or w_up.dtype != h.dtype or w_down.dtype != h.dtype:
+        if w_up.shape != (experts, rows_up, W) or (gated and rows_up % 2) or w_down.shape != (experts, W, ff) or w_up.dtype != h.dtype or w_down.dtype != h.dtype:
             raise KernelError("expert matrices must be [experts, ff, W] and [experts, W, ff] of the input's dtype")
         offsets, pair_of, ntiles, tile_expert, tile_row0 = plan
         hid = torch.empty((pairs, ff), dtype=h.dtype, device=h.device)
         y = torch.empty((pairs, W), dtype=torch.float32, device=h.device)
         _check(lib, lib.vapi_moe_grouped(_p(h), ctypes.c_longlong(h.stride(0)), _p(w_up), _dt(h), _p(ntiles), _p(tile_expert),
-                                         _p(tile_row0), _p(offsets), _p(pair_of), _p(wts), _p(hid), pairs, experts, ff, W,
-                                         top, 0, _stream()))
+                                         _p(tile_row0), _p(offsets), _p(pair_of), _p(wts), _p(hid), pairs, experts, rows_up, W,
+                                         top, 2 if gated else 0, _stream()))
         _check(lib, lib.vapi_moe_grouped(_p(hid), ctypes.c_longlong(ff), _p(w_down), _dt(h), _p(ntiles), _p(tile_expert),
                                          _p(tile_row0), _p(offsets), _p(pair_of), _p(wts), _p(y), pairs, experts, W, ff,
                                          top, 1, _stream()))
@@ -1540,4 +1572,71 @@ def moe_experts(h: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, plan, w_u
     out = torch.empty_like(h)
     _check(lib, lib.vapi_moe_combine(_p(y), _p(ids), _p(wts), _p(h), _p(shared), _p(out), _dt(h), n, W, top, experts,
                                      _stream()))
+    return out
+
+
+# ---------------------------------------------------------------------------------------
+# mixers whose state is a decayed sum of outer products: the matrix memory (mLSTM) and gated linear attention
+def _linear_memory_args(qkv, nh, dk, dv, state, need, state_slots, cu_q, positions):
+    _cuda(qkv, state, state_slots, cu_q, positions)
+    for t, w in ((state_slots, "state slots"), (cu_q, "cu_q"), (positions, "positions")):
+        _i32(t, w)
+    if qkv.dim() != 2 or qkv.stride(1) != 1 or qkv.shape[1] < 2 * nh * dk + nh * dv:
+        raise KernelError(f"q|k|v needs {2 * nh * dk + nh * dv} columns with unit inner stride")
+    if state.dtype != torch.float32 or state.dim() != 2 or state.stride(1) != 1 or state.shape[1] < need:
+        raise KernelError(f"the state must be float32 [slots, >= {need}] with unit inner stride")
+
+
+def matrix_memory(qkv: torch.Tensor, gates: torch.Tensor, gate_bias: Optional[torch.Tensor], cap: float, state: torch.Tensor,
+                  state_slots: torch.Tensor, cu_q: torch.Tensor, positions: torch.Tensor, nh: int, dk: int, dv: int,
+                  q_scale: float, floor_eps: float = 1e-6, status: Optional[torch.Tensor] = None,
+                  max_q: int = 1 << 30) -> torch.Tensor:
+    """The matrix memory of the mLSTM over every sequence of the step.  ``qkv`` [n, >= 2*nh*dk + nh*dv] (unit inner
+    stride, any row stride) holds q heads, k heads (``nh`` of ``dk``) and v heads (``nh`` of ``dv``); ``gates``
+    [n, 2*nh] float32 (unit inner stride) the pre-activations of the input gates, then of the forget gates, and
+    ``gate_bias`` [2*nh] what is added to them.  Per head, with ``li = cap tanh(a_i / cap)``,
+    ``lf = logsigmoid(cap tanh(a_f / cap))`` and a running maximum m that starts at 0:
+    ``m' = max(lf + m, li); S <- exp(lf + m - m') S + exp(li - m') k v^T``, n likewise with k alone, and
+    ``o = S^T (q_scale q) / (max(|n . q_scale q|, exp(-m')) + floor_eps)``.  ``state`` [slots, >= nh*dk*dv + nh*dk + nh]
+    float32 carries S [nh, dk, dv], n [nh, dk] and m [nh].  Returns o [n, nh*dv] float32."""
+    need = nh * dk * dv + nh * dk + nh
+    _linear_memory_args(qkv, nh, dk, dv, state, need, state_slots, cu_q, positions)
+    _cuda(gates, gate_bias)
+    _f32(gate_bias, "gate bias")
+    n = qkv.shape[0]
+    if gates.dtype != torch.float32 or gates.shape != (n, 2 * nh) or gates.stride(1) != 1:
+        raise KernelError("the gates must be float32 [n, 2*heads] with unit inner stride")
+    if gate_bias is not None and gate_bias.numel() != 2 * nh:
+        raise KernelError("the gates' bias must have 2*heads elements")
+    out = torch.empty((n, nh * dv), dtype=torch.float32, device=qkv.device)
+    lib = _lib("linear_memory")
+    _check(lib, lib.vapi_matrix_memory(
+        _p(qkv), ctypes.c_longlong(qkv.stride(0)), 0, nh * dk, 2 * nh * dk, _dt(qkv), _p(gates),
+        ctypes.c_longlong(gates.stride(0)), _p(gate_bias), ctypes.c_float(cap), ctypes.c_float(q_scale),
+        ctypes.c_float(floor_eps), _p(state), ctypes.c_longlong(state.stride(0)), _p(state_slots), _p(cu_q), _p(positions),
+        _p(out), cu_q.numel() - 1, nh, dk, dv, state.shape[0], int(min(max_q, 1 << 30)), _p(status), _stream()))
+    return out
+
+
+def gated_linear_attention(qkv: torch.Tensor, decay_logits: torch.Tensor, tau: float, state: torch.Tensor,
+                           state_slots: torch.Tensor, cu_q: torch.Tensor, positions: torch.Tensor, nh: int, dk: int, dv: int,
+                           q_scale: float, status: Optional[torch.Tensor] = None, max_q: int = 1 << 30) -> torch.Tensor:
+    """Gated linear attention over every sequence of the step.  ``qkv`` as for :func:`matrix_memory`;
+    ``decay_logits`` [n, nh*dk] float32 (unit inner stride) holds z, and key channel r of a head decays by
+    ``alpha = sigmoid(z)^(1/tau)``: ``S <- diag(alpha) S + k v^T; o = S^T (q_scale q)``.  ``state``
+    [slots, >= nh*dk*dv] float32 carries S [nh, dk, dv].  Returns o [n, nh*dv] float32."""
+    _linear_memory_args(qkv, nh, dk, dv, state, nh * dk * dv, state_slots, cu_q, positions)
+    _cuda(decay_logits)
+    n = qkv.shape[0]
+    if decay_logits.dtype != torch.float32 or decay_logits.shape != (n, nh * dk) or decay_logits.stride(1) != 1:
+        raise KernelError("the decay's logits must be float32 [n, heads*dk] with unit inner stride")
+    if not tau > 0:
+        raise KernelError("tau must be positive")
+    out = torch.empty((n, nh * dv), dtype=torch.float32, device=qkv.device)
+    lib = _lib("linear_memory")
+    _check(lib, lib.vapi_gated_linear_attention(
+        _p(qkv), ctypes.c_longlong(qkv.stride(0)), 0, nh * dk, 2 * nh * dk, _dt(qkv), _p(decay_logits),
+        ctypes.c_longlong(decay_logits.stride(0)), ctypes.c_float(1.0 / tau), ctypes.c_float(q_scale), _p(state),
+        ctypes.c_longlong(state.stride(0)), _p(state_slots), _p(cu_q), _p(positions), _p(out), cu_q.numel() - 1, nh, dk, dv,
+        state.shape[0], int(min(max_q, 1 << 30)), _p(status), _stream()))
     return out

@@ -2,7 +2,7 @@
 from .base import (CacheView, FeedForward, Mixer, Norm, NormedStream, PagedBuffer, PagedSpec, PostNormed, StreamState, Part, PositionEncoding, StateSpec,
                    TensorSpec, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS, make_part,
                    register_feed_forward, register_mixer, register_norm, register_position_encoding)
-from .norm import LayerNorm, RMSNorm
+from .norm import LayerNorm, NoNorm, RMSNorm
 from .rope import RotaryEncoding, ScaledRotaryEncoding
 from .attention import GQAttention
 from .shortconv import ShortConv
@@ -13,6 +13,7 @@ from .embedding import OutputHead, TokenEmbedding
 from .block import BLOCKS, PreNormBlock, SandwichBlock, register_block
 from .hyper import HyperBlock, HyperPending
 from .parallel import ParallelMixer
+from .linear_memory import GatedLinearAttentionMixer, MatrixMemoryMixer
 
 __all__ = [
     "CacheView", "FeedForward", "Mixer", "Norm", "NormedStream", "PagedBuffer", "PagedSpec", "StreamState", "Part", "PositionEncoding", "StateSpec",
@@ -21,4 +22,5 @@ __all__ = [
     "register_block", "RMSNorm", "RotaryEncoding", "GQAttention", "ShortConv", "SwiGLU", "OutputHead",
     "TokenEmbedding", "PreNormBlock", "SandwichBlock", "PostNormed", "ScaledRotaryEncoding", "GatedDeltaMixer", "Mamba2Mixer",
     "LayerNorm", "RGLRUMixer", "SparseMoE", "HyperBlock", "HyperPending", "ParallelMixer",
+    "NoNorm", "MatrixMemoryMixer", "GatedLinearAttentionMixer",
 ]

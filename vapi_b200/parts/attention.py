@@ -27,6 +27,8 @@ class GQAttention(Mixer):
     softmax's denominator), ``head_gate`` (head h's output times ``sigmoid(W_g x)_h``, the gate's
     rows riding on the fused projection), ``keep_first`` (with a window: the first ``keep_first`` tokens of a
     sequence stay visible to every later query, at their true positions; the pages are then all kept),
+    ``qk_norm`` ("head": the q/k norms run per head with a weight of ``head_dim``; "projection": over a token's
+    whole q, and whole k, before they are split into heads, with a weight per element of the projection),
     ``out_gate`` (the concatenated heads times ``sigmoid(W_g x)`` element by element, a gate as wide as the
     heads' output, its rows riding on the fused projection too), ``rope_layout`` ("half": pairs (i, i + rot/2);
     "interleaved": pairs (2i, 2i+1)) and ``weight_suffix`` (what follows a projection's name in the
@@ -40,7 +42,8 @@ class GQAttention(Mixer):
                  rot_dim: Optional[int] = None, window: int = 0, bias: bool = False,
                  scale: Optional[float] = None, names: Optional[Dict[str, str]] = None,
                  v_head_dim: Optional[int] = None, chunk: int = 0, sink: bool = False, head_gate: bool = False,
-                 rope_layout: str = "half", weight_suffix: str = ".weight", keep_first: int = 0, out_gate: bool = False):
+                 rope_layout: str = "half", weight_suffix: str = ".weight", keep_first: int = 0, out_gate: bool = False,
+                 qk_norm: str = "head"):
         if n_heads <= 0 or n_kv_heads <= 0 or n_heads % n_kv_heads:
             raise ValueError(f"{n_heads} heads are not a multiple of {n_kv_heads} kv heads")
         if rope_layout not in ("half", "interleaved"):
@@ -49,10 +52,13 @@ class GQAttention(Mixer):
         self.chunk, self.sink, self.head_gate = int(chunk), bool(sink), bool(head_gate)
         self.interleaved = rope_layout == "interleaved"
         self.keep_first, self.out_gate = max(int(keep_first), 0) if int(window) > 0 else 0, bool(out_gate)
+        if qk_norm not in ("head", "projection"):
+            raise ValueError(f"q/k norm `{qk_norm}` is not one of head, projection")
+        self.whole_norm = qk_norm == "projection" and qk_norm_eps is not None
         if self.head_gate and self.out_gate:
             raise ValueError("a gate per head and a gate per element exclude one another")
         self.general = bool(self.dv != int(head_dim) or self.chunk > 0 or self.sink or self.head_gate or self.interleaved
-                            or self.keep_first > 0 or self.out_gate)
+                            or self.keep_first > 0 or self.out_gate or self.whole_norm)
         if self.general:
             if head_dim % 4 or self.dv % 4 or not (4 <= head_dim <= 256 and 4 <= self.dv <= 256):
                 raise ValueError(f"head sizes {head_dim} / {self.dv} must be multiples of 4 in 4..256")
@@ -94,8 +100,8 @@ class GQAttention(Mixer):
                       TensorSpec(f"{prefix}{n['v']}.bias", (nkv * self.dv,), role="vector"),
                       TensorSpec(f"{prefix}{n['o']}.bias", (h,), role="vector")]
         if self.qk_norm_eps is not None:
-            specs += [TensorSpec(f"{prefix}{n['q_norm']}{x}", (d,), role="vector", init="ones"),
-                      TensorSpec(f"{prefix}{n['k_norm']}{x}", (d,), role="vector", init="ones")]
+            specs += [TensorSpec(f"{prefix}{n['q_norm']}{x}", (nh * d if self.whole_norm else d,), role="vector", init="ones"),
+                      TensorSpec(f"{prefix}{n['k_norm']}{x}", (nkv * d if self.whole_norm else d,), role="vector", init="ones")]
         return specs
 
     def bind(self, tensors, prefix, dtype):
@@ -187,7 +193,7 @@ class GQAttention(Mixer):
         ops.qk_norm_rope_write_split(qkv, nh, nkv, d, dv, self.q_w, self.k_w,
                                      self.qk_norm_eps if self.qk_norm_eps is not None else 0.0, cos, sin, self.rot_dim,
                                      self.interleaved, pages if cache.write else None, page_size, grp.slot_mapping,
-                                     ctx.status)
+                                     ctx.status, whole=self.whole_norm)
         gate = None
         if self.head_gate:
             off = (nh + nkv) * d + nkv * dv

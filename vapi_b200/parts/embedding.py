@@ -14,21 +14,32 @@ class TokenEmbedding(Part):
     (crates/vapi-backend-candle/src/models/lfm2.rs:675, 808).  Starts the float32 stream."""
 
     def __init__(self, vocab: int, hidden: int, name: str = "model.embed_tokens.weight", *,
-                 sinusoid_base: Optional[float] = None, streams: Optional[int] = None):
+                 sinusoid_base: Optional[float] = None, streams: Optional[int] = None,
+                 position_table: Optional[str] = None, positions: int = 0):
         self.vocab, self.hidden, self.name = int(vocab), int(hidden), name
         #: with ``sinusoid_base`` a position vector is added: entry 2i is sin(p * base^(-2i/hidden)), entry
         #: 2i+1 the cosine of the same angle (positions and angles in float32)
         self.sinusoid_base = float(sinusoid_base) if sinusoid_base is not None else None
         #: with ``streams`` the stream starts as that many equal copies, [n, streams, hidden]
         self.streams = int(streams) if streams is not None else None
+        #: with ``position_table`` (a tensor name) row p of that [positions, hidden] table is added at position p
+        self.position_table, self.positions = position_table, int(positions)
+        if position_table is not None and self.positions <= 0:
+            raise ValueError("a position table needs its number of rows")
         self.table: Optional[torch.Tensor] = None
         self.freq: Optional[torch.Tensor] = None
+        self.pos_rows: Optional[torch.Tensor] = None
 
     def tensor_specs(self, prefix: str = "") -> List[TensorSpec]:
-        return [TensorSpec(self.name, (self.vocab, self.hidden))]
+        specs = [TensorSpec(self.name, (self.vocab, self.hidden))]
+        if self.position_table is not None:
+            specs.append(TensorSpec(self.position_table, (self.positions, self.hidden)))
+        return specs
 
     def bind(self, tensors, prefix, dtype):
         self.table = tensors[self.name].contiguous()
+        if self.position_table is not None:
+            self.pos_rows = tensors[self.position_table].to(self.table.dtype).contiguous()
         if self.sinusoid_base is not None:
             i = torch.arange((self.hidden + 1) // 2, dtype=torch.float64)
             freq = torch.pow(torch.tensor(self.sinusoid_base, dtype=torch.float64), -2.0 * i / self.hidden)
@@ -36,10 +47,12 @@ class TokenEmbedding(Part):
 
     def forward(self, ctx: Any, next_weight: Optional[torch.Tensor] = None):
         """The stream; with ``next_weight`` also what a deferred norm needs: ``(x, ss, xw)``."""
-        if self.sinusoid_base is not None or self.streams is not None:
+        if self.sinusoid_base is not None or self.streams is not None or self.pos_rows is not None:
             if next_weight is not None:
                 raise ValueError("an embedding with positions or several streams has no deferred-norm form")
-            return ops.embed_sinusoid(self.table, ctx.tokens, ctx.positions, self.freq, self.streams or 1, ctx.status)
+            x = ops.embed_sinusoid(self.table, ctx.tokens, ctx.positions, self.freq, self.streams or 1, ctx.status,
+                                   pos_table=self.pos_rows)
+            return x if self.streams is not None else x.view(x.shape[0], self.hidden)
         return ops.embed(self.table, ctx.tokens, ctx.status, next_weight)
 
 

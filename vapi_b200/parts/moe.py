@@ -19,12 +19,17 @@ class SparseMoE(FeedForward):
     can be chosen.  The last ``identity`` outputs have no tensors: their output is the token's input itself.  A
     shared expert of the same form (``shared_ff`` wide; None: absent) runs for every token and is added.
 
+    Options: ``gated`` (an expert is ``W_down (silu(W_gate f) * (W_up f))``, three matrices), ``router_bias`` (a
+    stored vector added to the router's logits) and ``score`` "chosen" (the ``top`` largest logits win and the
+    weights are the softmax over the chosen logits only; there is then no correction tensor and no grouping).
+
     The experts' matrices are stacked at bind time ([experts, ff, hidden] and [experts, hidden, ff]); a step's
     tokens are grouped by expert on the device (see ``csrc/moe.cu``), so nothing about the routing reaches the host.
     """
 
     def __init__(self, hidden: int, ff: int, experts: int, top: int, *, identity: int = 0, groups: int = 1, keep: int = 1,
-                 shared_ff: Optional[int] = None, names: Optional[Dict[str, str]] = None, weight_suffix: str = ".weight"):
+                 shared_ff: Optional[int] = None, names: Optional[Dict[str, str]] = None, weight_suffix: str = ".weight",
+                 gated: bool = False, router_bias: bool = False, score: str = "softmax"):
         outputs = int(experts) + int(identity)
         if experts < 0 or identity < 0 or outputs <= 0 or not 1 <= top <= outputs:
             raise ValueError(f"{experts} experts + {identity} identity experts, top {top}")
@@ -32,23 +37,35 @@ class SparseMoE(FeedForward):
             raise ValueError(f"{outputs} router outputs in {groups} groups, {keep} kept, top {top}")
         self.hidden, self.ff, self.E, self.I, self.top = int(hidden), int(ff), int(experts), int(identity), int(top)
         self.groups, self.keep, self.shared_ff, self.sfx = int(groups), int(keep), shared_ff, weight_suffix
-        self.names = {"expert": "experts.{}.", "up": "up_proj", "down": "down_proj", "router": "router",
-                      "correction": "correction", "shared": "shared."}
+        if score not in ("softmax", "chosen"):
+            raise ValueError(f"score `{score}` is not one of softmax, chosen")
+        if score == "chosen" and (groups != 1 or identity):
+            raise ValueError("weights from the chosen logits come without groups and identity experts")
+        self.gated, self.router_bias, self.score = bool(gated), bool(router_bias), score
+        self.names = {"expert": "experts.{}.", "up": "up_proj", "down": "down_proj", "gate": "gate_proj", "router": "router",
+                      "correction": "correction", "router_bias": "router.bias", "shared": "shared."}
         if names:
             self.names.update(names)
-        self.router = self.correction = self.w_up = self.w_down = self.s_up = self.s_down = None
+        self.router = self.correction = self.bias = self.w_up = self.w_down = self.s_up = self.s_down = self.s_gate = None
 
     def tensor_specs(self, prefix: str) -> List[TensorSpec]:
         n, h, x = self.names, self.hidden, self.sfx
         specs = []
         for e in range(self.E):
             ep = prefix + n["expert"].format(e)
+            if self.gated:
+                specs.append(TensorSpec(f"{ep}{n['gate']}{x}", (self.ff, h)))
             specs += [TensorSpec(f"{ep}{n['up']}{x}", (self.ff, h)), TensorSpec(f"{ep}{n['down']}{x}", (h, self.ff))]
         # the router works in float32 whatever the activation dtype
-        specs += [TensorSpec(f"{prefix}{n['router']}{x}", (self.E + self.I, h), role="vector"),
-                  TensorSpec(f"{prefix}{n['correction']}", (self.E + self.I,), role="vector", init="zeros")]
+        specs.append(TensorSpec(f"{prefix}{n['router']}{x}", (self.E + self.I, h), role="vector"))
+        if self.score == "softmax":
+            specs.append(TensorSpec(f"{prefix}{n['correction']}", (self.E + self.I,), role="vector", init="zeros"))
+        if self.router_bias:
+            specs.append(TensorSpec(f"{prefix}{n['router_bias']}", (self.E + self.I,), role="vector"))
         if self.shared_ff is not None:
             sp = prefix + n["shared"]
+            if self.gated:
+                specs.append(TensorSpec(f"{sp}{n['gate']}{x}", (self.shared_ff, h)))
             specs += [TensorSpec(f"{sp}{n['up']}{x}", (self.shared_ff, h)), TensorSpec(f"{sp}{n['down']}{x}", (h, self.shared_ff))]
         return specs
 
@@ -58,20 +75,31 @@ class SparseMoE(FeedForward):
             ups = [tensors[f"{prefix}{n['expert'].format(e)}{n['up']}{x}"] for e in range(self.E)]
             downs = [tensors[f"{prefix}{n['expert'].format(e)}{n['down']}{x}"] for e in range(self.E)]
             self.w_up = torch.stack([t.to(dtype) for t in ups], 0).contiguous()
+            if self.gated:
+                # rows alternate gate_j, up_j, so that a thread of the product holds a pair and applies the gate itself
+                gates = torch.stack([tensors[f"{prefix}{n['expert'].format(e)}{n['gate']}{x}"].to(dtype) for e in range(self.E)], 0)
+                self.w_up = torch.stack([gates, self.w_up], 2).reshape(self.E, 2 * self.ff, self.hidden).contiguous()
             self.w_down = torch.stack([t.to(dtype) for t in downs], 0).contiguous()
         self.router = tensors[f"{prefix}{n['router']}{x}"].contiguous()
-        self.correction = tensors[f"{prefix}{n['correction']}"].contiguous()
+        self.correction = tensors[f"{prefix}{n['correction']}"].contiguous() if self.score == "softmax" else None
+        self.bias = tensors[f"{prefix}{n['router_bias']}"].contiguous() if self.router_bias else None
         if self.shared_ff is not None:
             sp = prefix + n["shared"]
             self.s_up = tensors[f"{sp}{n['up']}{x}"].contiguous()
             self.s_down = tensors[f"{sp}{n['down']}{x}"].contiguous()
+            if self.gated:
+                g = tensors[f"{sp}{n['gate']}{x}"]
+                self.s_gate = torch.cat([g.to(self.s_up.dtype), self.s_up], 0).contiguous()      # gate | up, one product
 
     def forward(self, f: torch.Tensor, ctx: Any) -> torch.Tensor:
-        ids, wts, plan = ops.moe_route(f, self.router, self.correction, self.E, self.top, self.groups, self.keep)
+        ids, wts, plan = ops.moe_route(f, self.router, self.correction, self.E, self.top, self.groups, self.keep,
+                                       bias=self.bias, score=self.score)
         shared = None
-        if self.s_up is not None:
+        if self.s_gate is not None:
+            shared = ops.linear(ops.linear_swiglu(f, self.s_gate), self.s_down)
+        elif self.s_up is not None:
             shared = ops.linear(ops.relu_squared(ops.linear(f, self.s_up)), self.s_down)
-        return ops.moe_experts(f, ids, wts, plan, self.w_up, self.w_down, shared)
+        return ops.moe_experts(f, ids, wts, plan, self.w_up, self.w_down, shared, gated=self.gated)
 
 
 register_feed_forward("sparse_moe", SparseMoE)

@@ -76,5 +76,29 @@ class LayerNorm(Norm):
                                    delta.branch if delta is not None else None)
 
 
+class NoNorm(Norm):
+    """No norm at all, for a sublayer that reads the residual stream as it is: ``apply`` folds in what is pending
+    (a plain delta, or a :class:`PostNormed` that is normed on its way into the stream) and hands the rows on in
+    the activation dtype.  It has no tensors."""
+
+    kind = "none"
+
+    def __init__(self, dim: int = 0):
+        self.dim = int(dim)
+        self.weight = None
+
+    def apply(self, x, delta, dtype, rows=None):
+        if isinstance(delta, PostNormed):
+            return ops.postnorm_add_rmsnorm(x, delta.y, delta.weight, delta.eps, delta.mult, None, 0.0, dtype, rows, copy=True)
+        if delta is not None:
+            if rows is not None:
+                raise ValueError("a plain delta is added to every row or to none")
+            ops.add_residual(x, delta)
+        if rows is None and x.dtype == dtype:
+            return x                      # the sublayers only read it
+        return ops.postnorm_add_rmsnorm(x, None, None, 0.0, 1.0, None, 0.0, dtype, rows, copy=True)
+
+
+register_norm("none", NoNorm)
 register_norm("rmsnorm", RMSNorm)
 register_norm("layernorm", LayerNorm)

@@ -93,7 +93,8 @@ def load_tensors(model_dir: str, specs: Iterable[TensorSpec], dtype: torch.dtype
     for s in specs:
         if s.name in where:
             got = tuple(handles[where[s.name]].get_slice(s.name).get_shape())
-            if got != tuple(s.shape):
+            # (a dimension the plan leaves open, -1, is a size that only the checkpoint gives)
+            if len(got) != len(s.shape) or any(w != -1 and g != w for g, w in zip(got, s.shape)):
                 wrong.append((s.name, got, tuple(s.shape)))
     if missing or unexpected or wrong:
         raise WeightError(model_dir, missing, unexpected, wrong)

@@ -34,6 +34,9 @@ def random_tensors(plan, seed: int, std: float = 0.02, norm_init: str = "ones",
     out: Dict[str, torch.Tensor] = {}
     dev = str(torch.device(device))
     for spec in plan.tensor_specs():
+        if any(d < 0 for d in spec.shape):
+            raise ValueError(f"tensor `{spec.name}` has a size that only a checkpoint gives; the configuration must name it "
+                             f"before random weights can be drawn")
         g = _gen(seed, spec.name, dev)
         if spec.role == "table":
             out[spec.name] = torch.zeros(spec.shape, dtype=torch.int32, device=dev)

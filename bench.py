@@ -200,7 +200,7 @@ OPS = {"embed": "elementwise", "add_residual_ss": "elementwise", "resolve_tokens
        "causal_conv_silu": "recurrent", "gated_delta": "recurrent", "state_space": "recurrent",
        "embed_sinusoid": "hyper", "hyper_read_norm": "hyper", "branch_rmsnorm_mean": "hyper", "sigmoid_gate": "hyper",
        "softcap": "hyper", "causal_conv": "recurrent", "rglru": "rglru", "relu_squared": "moe", "moe_route": "moe",
-       "moe_experts": "moe"}
+       "moe_experts": "moe", "matrix_memory": "linear_memory", "gated_linear_attention": "linear_memory"}
 
 
 class OpLog:
@@ -781,8 +781,35 @@ def rapolix_sizes(name):
     return rp, lf
 
 
+def demazen_sizes(name):
+    """Demazen layers at the widths of LFM2-<name>: the matrix memory with heads of 128 x 256 (keys half as wide as
+    the model in all, values as wide as it); attention with the same heads as the LFM2 stack (keys and values of 64, q
+    and k normed over their whole projections, no rotation) over a window of 1,024 beside gated linear attention
+    with four heads of 128 x 256 and a decay through a pair of rank 16; feed-forwards alternate between a dense one of
+    the LFM2 stack's width and a mixture of 32 experts (a quarter of that width each, four of them a token); learned
+    positions; eight layers, the last two running the weights of the two before them.  Beside it Vukavik (the
+    matrix-state recurrences of the package: gated delta rule, Mamba-2) and Rapolix (window attention beside a
+    recurrence, experts) at the same widths."""
+    from vapi_b200.models.lfm2 import Lfm2Config
+    lf = lfm2_sizes(name)
+    W, ff = lf["hidden_size"], Lfm2Config.effective_ff_dim(lf)
+    dense = {"kind": "dense", "ff": ff}
+    sparse = {"kind": "moe", "expert": {"ff": ff // 4}, "router": {"experts": 32, "top": 4}}
+    memory = {"heads": W // 256, "dim": 128, "vdim": 256, "gate_cap": 15.0}
+    par = {"left": {"heads": lf["num_attention_heads"], "kv_heads": lf["num_key_value_heads"], "dim": 64, "vdim": 64,
+                    "scale": 0.125, "mask": {"size": 1024}},
+           "right": {"heads": 4, "dim": 128, "vdim": 256, "tau": 16.0, "rank": 16}}
+    layers = [{"type": "mlstm", "mixer": memory, "mlp": dense}, {"type": "parallel", "mixer": par, "mlp": sparse},
+              {"type": "mlstm", "mixer": memory, "mlp": sparse}, {"type": "parallel", "mixer": par, "mlp": dense}] * 2
+    layers[6], layers[7] = dict(layers[6], weights_of=4), dict(layers[7], weights_of=5)
+    dz = {"architecture": "Demazen", "vocab": lf["vocab_size"], "width": W, "max_positions": 8192, "logit_softcap": 30.0,
+          "norm": {"eps": 1e-5}, "layers": layers}
+    return dz, vukavik_sizes(name)[0], rapolix_sizes(name)[0]
+
+
 def mixers(args):
-    """``--only mixers``: prefill and decode of eight layers of ``--design`` (Vukavik or Rapolix) beside LFM2 layers
+    """``--only mixers``: prefill and decode of eight layers of ``--design`` beside LFM2 layers (Vukavik, Rapolix; Demazen
+    stands beside Vukavik and Rapolix, whose kernels are the nearest to its own)
     of equal width (random weights), and where each model's time goes, kernel family by kernel family."""
     import torch
     from vapi_b200 import ops
@@ -796,9 +823,14 @@ def mixers(args):
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
     out = {"only": "mixers", "sizes": args.sizes, "dtype": "bfloat16", "prefill_tokens": T, "decode_batch": B,
            "decode_context": ctx_len, "peaks": pk, "models": {}}
-    vk, lf = rapolix_sizes(args.sizes) if args.design == "rapolix" else vukavik_sizes(args.sizes)
     out["design"] = args.design
-    for name, cfg in ((args.design, vk), ("lfm2", lf)):
+    if args.design == "demazen":
+        dz, vk, rp = demazen_sizes(args.sizes)
+        models = (("demazen", dz), ("vukavik", vk), ("rapolix", rp))
+    else:
+        vk, lf = rapolix_sizes(args.sizes) if args.design == "rapolix" else vukavik_sizes(args.sizes)
+        models = ((args.design, vk), ("lfm2", lf))
+    for name, cfg in models:
         vocab = cfg.get("vocab") or cfg["vocab_size"]
         n_pages = (B + 1) * (-(-(ctx_len + 64) // page)) + 8
         runner = ModelRunner.from_random(cfg, seed=0, dtype="bfloat16", device="cuda:0", num_pages=n_pages, page_size=page,
@@ -857,6 +889,10 @@ def mixers(args):
                 mix_flops["gated_delta"] = 2.0 * 4 * m.nh * m.dk * m.dv * T      # decay, S^T k, the rank-one write, S^T q
             elif kind == "Mamba2Mixer":
                 mix_flops["state_space"] = 2.0 * 3 * m.nh * m.N * m.p * T        # decay, the rank-one write, S^T C
+            elif kind == "MatrixMemoryMixer":
+                mix_flops["matrix_memory"] = 2.0 * 3 * m.nh * m.dk * m.dv * T    # decay, the rank-one write, S^T q
+            elif kind == "GatedLinearAttentionMixer":
+                mix_flops["gated_linear_attention"] = 2.0 * 3 * m.nh * m.dk * m.dv * T
         rows = {}
         for k, f in sorted(fam.items(), key=lambda kv: -kv[1]["ms"]):
             row = {"ms": round(f["ms"], 3), "calls": f["calls"]}
@@ -957,8 +993,8 @@ def main():
                          "and print what one step's kernels did inside the captured graph, or (mixers) prefill and "
                          "decode of eight Vukavik layers beside eight LFM2 layers of equal width, kernel family by kernel family")
     ap.add_argument("--sizes", default="1.2b", choices=["1.2b", "700m", "2.6b"], help="layer sizes of LFM2-<sizes>")
-    ap.add_argument("--design", default="vukavik", choices=["vukavik", "rapolix"],
-                    help="with --only mixers: the architecture whose layers stand beside LFM2's")
+    ap.add_argument("--design", default="vukavik", choices=["vukavik", "rapolix", "demazen"],
+                    help="with --only mixers: the architecture whose layers stand beside LFM2's (demazen: beside Vukavik's and Rapolix's)")
     ap.add_argument("--page-size", type=int, default=0, help="tokens per cache page (0: the engine's default)")
     ap.add_argument("--dtype", default="bfloat16", help="bfloat16 (serving) or float32 (the true 32-bit path)")
     ap.add_argument("--no-fp32", action="store_true", help="leave the float32 points out of the default run")

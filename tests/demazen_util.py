@@ -4,6 +4,7 @@ from __future__ import annotations
 import zlib
 from typing import Dict, Optional, Sequence, Tuple
 
+import numpy as np
 import torch
 
 import plain_demazen as plain
@@ -150,11 +151,25 @@ class Oracle:
         self.cfg = plain.read_config(folder)
         self.w = plain.read_weights(folder, torch.float64)
         self._memo: Dict[Tuple[int, ...], torch.Tensor] = {}
+        self.w32 = None
 
     def logits(self, tokens: Sequence[int]) -> torch.Tensor:
         key = tuple(tokens)
         if key not in self._memo:
             self._memo[key] = plain.forward(self.cfg, self.w, tokens)
+        return self._memo[key]
+
+    def rounding(self, tokens: Sequence[int]) -> np.ndarray:
+        """What 32-bit arithmetic alone does to each position's logits: the plain model in float32 against itself
+        in float64, as a part of the logits' range.  (Where a memory's read-out is small beside its terms, or a norm
+        divides by little, a position is ill-conditioned, and no order of summation is exact there.)"""
+        key = ("f32",) + tuple(tokens)
+        if key not in self._memo:
+            if self.w32 is None:
+                self.w32 = {k: (v.float() if v.is_floating_point() else v) for k, v in self.w.items()}
+            want = self.logits(tokens)
+            got = plain.forward(self.cfg, self.w32, tokens).double()
+            self._memo[key] = ((got - want).abs().amax(-1) / float(want.max() - want.min())).numpy()
         return self._memo[key]
 
     def greedy(self, tokens: Sequence[int], n: int):

@@ -46,7 +46,11 @@ def _check(runner, oracle, requests, schedule, dtype):
             assert e.mean() <= 0.02 and np.percentile(e, 95) <= vu.limit(dtype) and err <= 0.15, \
                 f"request {rid}: mean {e.mean():.3e}, 95th percentile {np.percentile(e, 95):.3e}, worst {err:.3e} at {pos}"
         else:
-            assert err <= vu.limit(dtype), f"request {rid}: {err:.3e} of the logit range at position {pos} of {len(toks)}"
+            # a position may be off by three times what float32 rounding does to the plain model there, or by the limit
+            e = np.abs(got[rid] - want.numpy()).max(-1) / float(want.max() - want.min())
+            over = e - np.maximum(vu.limit(dtype), 3.0 * oracle.rounding(toks))
+            pos = int(over.argmax())
+            assert over[pos] <= 0, f"request {rid}: {e[pos]:.3e} of the logit range at position {pos} of {len(toks)}"
 
 
 def _close(a, b, tol):

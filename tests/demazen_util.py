@@ -115,9 +115,15 @@ def planted_cache(klen: int, qlen: int, j_star: int, dk: int, dv: int, page: int
     return q.to(device, dtype).contiguous(), cache.to(device, dtype).contiguous(), order[None, :].to(device).contiguous()
 
 
-def write_model(folder: str, cfg: dict, seed: int = 0, dtype=torch.float32, std: float = 0.12) -> str:
+def write_model(folder: str, cfg: dict, seed: int = 0, dtype=torch.float32, std: float = 0.12, planted_routes: bool = False) -> str:
     """A model folder whose small parameters are far from their neutral values: gates that move and reach their cap,
-    decays from fast to slow, router biases of both signs, position vectors as large as the embeddings."""
+    decays from fast to slow, router biases of both signs, position vectors as large as the embeddings.
+
+    With ``planted_routes`` no router's choice is a close call, so that a model in reduced precision chooses as the
+    plain one does: the last channels of the width carry a code of the token (the embedding writes it, the position
+    vectors and every norm weight are zero there, so no sublayer adds to it), each expert's router row reads one of
+    these channels with a large weight, and two experts' logits are at least 2 apart whatever the other channels hold.
+    The chosen experts' weights still move with the random part of the rows and with the biases."""
     from vapi_b200.config.model import resolve_architecture
     from vapi_b200.weights import write_random_model
     arch = resolve_architecture(cfg)
@@ -141,6 +147,32 @@ def write_model(folder: str, cfg: dict, seed: int = 0, dtype=torch.float32, std:
             over[s.name] = 0.5 * torch.randn(s.shape, generator=g)
         elif tail == "mlp.router.b":
             over[s.name] = 0.5 * torch.randn(s.shape, generator=g)
+    if planted_routes:
+        W, V = cfg["width"], cfg["vocab"]
+        most = max([e["mlp"]["router"]["experts"] for e in cfg["layers"] if e.get("mlp") and e["mlp"]["kind"] == "moe"] or [0])
+        chan = list(range(W - most, W))
+        shape = {s.name: tuple(s.shape) for s in specs}
+
+        def drawn(name, scale, mean=0.0):
+            g = torch.Generator().manual_seed(seed * 104729 + zlib.crc32(name.encode()) % 100003)
+            return mean + scale * torch.randn(shape[name], generator=g)
+        emb, pos = drawn("embed", std), drawn("pos", std)
+        for j, c in enumerate(chan):                      # channel j of token t holds ((t + j) mod most) / 4: exact in bfloat16
+            emb[:, c] = ((torch.arange(V) + j) % most).float() * 0.25
+            pos[:, c] = 0.0
+        over["embed"], over["pos"] = emb, pos
+        for name in shape:
+            parts = name.split(".")
+            if len(parts) == 2 and parts[1] in ("norm1", "norm2"):
+                over[name] = drawn(name, 0.1, 1.0)
+                over[name][chan] = 0.0
+            elif name.endswith("mlp.router"):
+                r = drawn(name, 0.004)
+                for e in range(r.shape[0]):
+                    r[e, chan[(e + int(parts[0][1:])) % most]] = 8.0
+                over[name] = r
+            elif name.endswith("mlp.router.b"):
+                over[name] = drawn(name, 0.2)
     return write_random_model(folder, cfg, seed, std=std, norm_init="perturbed", dtype=dtype, overrides=over)
 
 
@@ -151,7 +183,6 @@ class Oracle:
         self.cfg = plain.read_config(folder)
         self.w = plain.read_weights(folder, torch.float64)
         self._memo: Dict[Tuple[int, ...], torch.Tensor] = {}
-        self.w32 = None
 
     def logits(self, tokens: Sequence[int]) -> torch.Tensor:
         key = tuple(tokens)
@@ -159,18 +190,39 @@ class Oracle:
             self._memo[key] = plain.forward(self.cfg, self.w, tokens)
         return self._memo[key]
 
-    def rounding(self, tokens: Sequence[int]) -> np.ndarray:
-        """What 32-bit arithmetic alone does to each position's logits: the plain model in float32 against itself
-        in float64, as a part of the logits' range.  (Where a memory's read-out is small beside its terms, or a norm
-        divides by little, a position is ill-conditioned, and no order of summation is exact there.)"""
-        key = ("f32",) + tuple(tokens)
+    def rounding(self, tokens: Sequence[int], dtype: str = "float32") -> np.ndarray:
+        """What reduced precision alone does to each position's logits, as a part of the logits' range.  float32: the
+        plain model in float32 against itself in float64, the largest of three draws (the weights as they are, and
+        twice with every element moved by up to 2^-23 of itself, so that the roundings fall otherwise): one draw of
+        an ill-conditioned position's error may be small by chance.  bfloat16: the plain model with every matrix and
+        table moved by up to 2^-8 of each element (as much as rounding its operands to bfloat16 moves a product)
+        against itself.  Where a memory's read-out is small beside its terms, a norm divides by little or a gate sits
+        on its steep part, a position is ill-conditioned, and no order of summation is exact there."""
+        key = (dtype,) + tuple(tokens)
         if key not in self._memo:
-            if self.w32 is None:
-                self.w32 = {k: (v.float() if v.is_floating_point() else v) for k, v in self.w.items()}
             want = self.logits(tokens)
-            got = plain.forward(self.cfg, self.w32, tokens).double()
-            self._memo[key] = ((got - want).abs().amax(-1) / float(want.max() - want.min())).numpy()
+            g = torch.Generator().manual_seed(99)
+
+            def moved(by, to):
+                return {k: (v * (1.0 + by * (2.0 * torch.rand(v.shape, generator=g, dtype=v.dtype) - 1.0))).to(to)
+                        if v.is_floating_point() and (v.dim() == 2 or to == torch.float32) else v for k, v in self.w.items()}
+            if dtype == "float32":
+                draws = [plain.forward(self.cfg, moved(by, torch.float32), tokens).double() for by in (0.0, 2.0 ** -23, 2.0 ** -23)]
+            else:
+                draws = [plain.forward(self.cfg, moved(2.0 ** -8, torch.float64), tokens)]
+            err = torch.stack([(got - want).abs().amax(-1) for got in draws]).amax(0)
+            self._memo[key] = (err / float(want.max() - want.min())).numpy()
         return self._memo[key]
+
+    def close_calls(self, tokens: Sequence[int], least: float = 0.02) -> np.ndarray:
+        """Positions at which some router's choice hangs on less than ``least`` of its logits' spread: reduced
+        precision may choose otherwise there, and nothing can be asked of such a position's logits."""
+        key = ("margin",) + tuple(tokens)
+        if key not in self._memo:
+            m: list = []
+            plain.forward(self.cfg, self.w, tokens, margins=m)
+            self._memo[key] = torch.stack(m).amin(0).numpy() if m else np.full(len(tokens), np.inf)
+        return self._memo[key] < least
 
     def greedy(self, tokens: Sequence[int], n: int):
         toks, out = list(tokens), []

@@ -135,9 +135,13 @@ def gated_ff(w, p: str, h: torch.Tensor) -> torch.Tensor:
     return (silu(h @ w[p + "gate"].T) * (h @ w[p + "up"].T)) @ w[p + "down"].T
 
 
-def experts(w, p: str, m: dict, h: torch.Tensor) -> torch.Tensor:
+def experts(w, p: str, m: dict, h: torch.Tensor, margins: Optional[List[torch.Tensor]] = None) -> torch.Tensor:
     top = m["router"]["top"]
     z = h @ w[p + "router"].T + w[p + "router.b"]
+    if margins is not None and top < z.shape[-1]:
+        # how far the last chosen logit stands above the first one left out, as a part of the logits' spread
+        zs = torch.sort(z, -1, descending=True).values
+        margins.append((zs[:, top - 1] - zs[:, top]) / (zs[:, 0] - zs[:, -1]).clamp_min(1e-30))
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         val, idx = torch.topk(z[t], top)
@@ -147,13 +151,15 @@ def experts(w, p: str, m: dict, h: torch.Tensor) -> torch.Tensor:
     return out
 
 
-def feed_forward(w, p: str, m: dict, h: torch.Tensor) -> torch.Tensor:
-    return gated_ff(w, p, h) if m["kind"] == "dense" else experts(w, p, m, h)
+def feed_forward(w, p: str, m: dict, h: torch.Tensor, margins: Optional[List[torch.Tensor]] = None) -> torch.Tensor:
+    return gated_ff(w, p, h) if m["kind"] == "dense" else experts(w, p, m, h, margins)
 
 
 # ---- the model -------------------------------------------------------------------------------------------
-def forward(cfg: dict, w, tokens: Sequence[int], layers_out: Optional[List[torch.Tensor]] = None) -> torch.Tensor:
-    """Logits [T, vocab] of a whole sequence from position 0."""
+def forward(cfg: dict, w, tokens: Sequence[int], layers_out: Optional[List[torch.Tensor]] = None,
+            margins: Optional[List[torch.Tensor]] = None) -> torch.Tensor:
+    """Logits [T, vocab] of a whole sequence from position 0.  ``layers_out`` receives the stream after every layer,
+    ``margins`` every routed layer's margin of choice per token."""
     eps = float(cfg["norm"]["eps"])
     x = embed(w, tokens)
     for i, e in enumerate(cfg["layers"]):
@@ -161,7 +167,7 @@ def forward(cfg: dict, w, tokens: Sequence[int], layers_out: Optional[List[torch
         mix = mlstm if e["type"] == "mlstm" else parallel
         x = x + rms(mix(w, p + "mix.", e["mixer"], x, eps), eps, w[p + "norm1"])
         if e.get("mlp") is not None:
-            x = x + rms(feed_forward(w, p + "mlp.", e["mlp"], x), eps, w[p + "norm2"])
+            x = x + rms(feed_forward(w, p + "mlp.", e["mlp"], x, margins), eps, w[p + "norm2"])
         if layers_out is not None:
             layers_out.append(x.clone())
     logits = rms(x, eps, w["final.norm"]) @ w["embed"].T

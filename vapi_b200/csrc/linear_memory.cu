@@ -27,6 +27,7 @@ using namespace vapi;
 
 constexpr int LM_THREADS = 128;
 constexpr int LM_MLSTM = 0, LM_GLA = 1;
+constexpr int LM_GROUP = 4;                                   // tokens whose sums over the rows are taken together
 
 __device__ __forceinline__ float lm_logsigmoid(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
 
@@ -36,6 +37,18 @@ __device__ __forceinline__ float lm_lanes_sum(float v) {
     for (int o = LPC >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
     return v;
 }
+
+// CH consecutive elements of a row vector as one thread brings them: with 16-byte loads where the addresses allow
+template <int BYTES> struct LmRaw;
+template <> struct __align__(8) LmRaw<8> { uint2 x; };
+template <> struct __align__(16) LmRaw<16> { uint4 x; };
+template <> struct __align__(16) LmRaw<32> { uint4 x, y; };
+template <typename T, int CH>
+union LmPiece {
+    LmRaw<CH * (int)sizeof(T)> raw;
+    T v[CH];
+    __device__ LmPiece() {}
+};
 
 template <typename T, int RT, int LPC, int MODE>
 struct LmShape {
@@ -49,8 +62,11 @@ struct LmShape {
     static constexpr int CB = CW * WARPS;                      // columns of S a block
     static constexpr int NV = MODE == LM_GLA ? 3 : 2;          // row vectors a token: k, q (, decay)
     static constexpr int NPT = TC * RP / LM_THREADS;           // row elements per thread and vector
+    static constexpr int CH = NPT >= 8 ? 8 : 4;                // of which so many lie side by side in one token's row
+    static constexpr int NCH = NPT / CH;
     static constexpr int VPT = (TC * CB + LM_THREADS - 1) / LM_THREADS;
     static_assert(RT % 4 == 0 && (TC * RP) % LM_THREADS == 0, "rows per lane come in fours");
+    static_assert(NPT % CH == 0 && RT % CH == 0, "a thread's piece lies within one lane's rows");
     static __device__ __forceinline__ int pad(int r) { return r + (r / RT) * 4; }
 };
 
@@ -60,9 +76,10 @@ linear_memory_kernel(const T* __restrict__ qkv, long long qkv_stride, int q_off,
                      const float* __restrict__ gates, long long gates_stride, const float* __restrict__ gate_bias,
                      float gate_param, float q_scale, float floor_eps, float* __restrict__ state, long long slot_stride,
                      const int* __restrict__ state_slots, const int* __restrict__ cu_q, const int* __restrict__ positions,
-                     float* __restrict__ out, int nh, int rows, int cols, int num_slots, int* __restrict__ status) {
+                     float* __restrict__ out, int nh, int rows, int cols, int num_slots, int wide_loads, int gates_are_decays,
+                     int* __restrict__ status) {
     using Sh = LmShape<T, RT, LPC, MODE>;
-    constexpr int TC = Sh::TC, RPP = Sh::RPP, RP = Sh::RP, CB = Sh::CB, NPT = Sh::NPT, VPT = Sh::VPT;
+    constexpr int TC = Sh::TC, RPP = Sh::RPP, RP = Sh::RP, CB = Sh::CB, VPT = Sh::VPT, CH = Sh::CH, NCH = Sh::NCH;
     __shared__ __align__(16) float sk[TC * RPP], sq[TC * RPP];
     __shared__ __align__(16) float sa[MODE == LM_GLA ? TC * RPP : 4];
     __shared__ float sv[TC * CB];
@@ -86,36 +103,55 @@ linear_memory_kernel(const T* __restrict__ qkv, long long qkv_stride, int q_off,
     float* S_glob = state + (size_t)slot * slot_stride + ((size_t)h * rows) * cols;
     float* n_glob = state + (size_t)slot * slot_stride + (size_t)nh * rows * cols + (size_t)h * rows;
     float* m_glob = state + (size_t)slot * slot_stride + (size_t)nh * rows * cols + (size_t)nh * rows + h;
-    const bool fresh = positions[t0] == 0;
     const float bias_i = (MODE == LM_MLSTM && gate_bias) ? gate_bias[h] : 0.f;
     const float bias_f = (MODE == LM_MLSTM && gate_bias) ? gate_bias[nh + h] : 0.f;
     pdl_wait();
+    // the state is asked for before it is known whether the sequence starts here, so that a decode step's loads
+    // (the slot's state and the position) are in flight together; a fresh sequence drops what came
     float S[RT];
 #pragma unroll
     for (int j = 0; j < RT; ++j) {
         S[j] = 0.f;
-        if (!fresh && r0 + j < rows) {
+        if (r0 + j < rows) {
             if (is_n) S[j] = n_glob[r0 + j];
             else if (col_ok) S[j] = S_glob[(size_t)(r0 + j) * cols + col];
         }
     }
-    float m_run = (MODE == LM_MLSTM && !fresh) ? *m_glob : 0.f;          // (every lane of the first warp carries it)
+    float m_run = MODE == LM_MLSTM ? *m_glob : 0.f;                      // (every lane of the first warp carries it)
+    const bool fresh = positions[t0] == 0;
+    if (fresh) {
+        m_run = 0.f;
+#pragma unroll
+        for (int j = 0; j < RT; ++j) S[j] = 0.f;
+    }
 
-    // the next round's inputs, in registers
-    T ra[NPT], rb[NPT], rv[VPT];
-    float rz[MODE == LM_GLA ? NPT : 1];
+    // the next round's inputs, in registers: a thread brings pieces of CH neighbouring rows of one token (piece j
+    // starts at element (threadIdx.x + j * LM_THREADS) * CH of the round's [TC, RP] rows)
+    LmPiece<T, CH> ra[NCH], rb[NCH];
+    LmPiece<float, CH> rz[MODE == LM_GLA ? NCH : 1];
+    T rv[VPT];
     float g_i = 0.f, g_f = 0.f;
     auto fetch = [&](int first) {
         const int count = min(TC, qlen - first);
 #pragma unroll
-        for (int e = 0; e < NPT; ++e) {
-            const int idx = threadIdx.x + e * LM_THREADS;
+        for (int j = 0; j < NCH; ++j) {
+            const int idx = (threadIdx.x + j * LM_THREADS) * CH;
             const int tt = idx / RP, r = idx - tt * RP;
-            const bool ok = tt < count && r < rows;
-            const T* row = qkv + (size_t)(t0 + first + tt) * qkv_stride;
-            ra[e] = ok ? row[k_off + h * rows + r] : from_f32<T>(0.f);
-            rb[e] = ok ? row[q_off + h * rows + r] : from_f32<T>(0.f);
-            if (MODE == LM_GLA) rz[e] = ok ? gates[(size_t)(t0 + first + tt) * gates_stride + h * rows + r] : 0.f;
+            const T* row = qkv + (size_t)(t0 + first + tt) * qkv_stride + h * rows + r;
+            const float* zrow = gates + (size_t)(t0 + first + tt) * gates_stride + h * rows + r;
+            if (wide_loads && tt < count && r < rows) {          // (rows is a multiple of CH then: the piece is whole)
+                ra[j].raw = *reinterpret_cast<const LmRaw<CH * (int)sizeof(T)>*>(row + k_off);
+                rb[j].raw = *reinterpret_cast<const LmRaw<CH * (int)sizeof(T)>*>(row + q_off);
+                if (MODE == LM_GLA) rz[j].raw = *reinterpret_cast<const LmRaw<CH * 4>*>(zrow);
+            } else {
+#pragma unroll
+                for (int i = 0; i < CH; ++i) {
+                    const bool ok = tt < count && r + i < rows;
+                    ra[j].v[i] = ok ? row[k_off + i] : from_f32<T>(0.f);
+                    rb[j].v[i] = ok ? row[q_off + i] : from_f32<T>(0.f);
+                    if (MODE == LM_GLA) rz[j].v[i] = ok ? zrow[i] : 0.f;
+                }
+            }
         }
 #pragma unroll
         for (int e = 0; e < VPT; ++e) {
@@ -134,12 +170,28 @@ linear_memory_kernel(const T* __restrict__ qkv, long long qkv_stride, int q_off,
         const int count = min(TC, qlen - first);
         __syncthreads();                                    // the steps of the last round have read shared memory
 #pragma unroll
-        for (int e = 0; e < NPT; ++e) {
-            const int idx = threadIdx.x + e * LM_THREADS;
+        for (int j = 0; j < NCH; ++j) {
+            const int idx = (threadIdx.x + j * LM_THREADS) * CH;
             const int tt = idx / RP, r = idx - tt * RP;
-            sk[tt * RPP + Sh::pad(r)] = to_f32(ra[e]);
-            sq[tt * RPP + Sh::pad(r)] = to_f32(rb[e]) * q_scale;
-            if (MODE == LM_GLA) sa[tt * RPP + Sh::pad(r)] = expf(lm_logsigmoid(rz[e]) * gate_param);
+            float4* dk = reinterpret_cast<float4*>(sk + tt * RPP + Sh::pad(r));
+            float4* dq = reinterpret_cast<float4*>(sq + tt * RPP + Sh::pad(r));
+            float4* da = reinterpret_cast<float4*>(sa + (MODE == LM_GLA ? tt * RPP + Sh::pad(r) : 0));
+#pragma unroll
+            for (int i = 0; i < CH; i += 4) {
+                dk[i / 4] = make_float4(to_f32(ra[j].v[i]), to_f32(ra[j].v[i + 1]), to_f32(ra[j].v[i + 2]), to_f32(ra[j].v[i + 3]));
+                dq[i / 4] = make_float4(to_f32(rb[j].v[i]) * q_scale, to_f32(rb[j].v[i + 1]) * q_scale,
+                                        to_f32(rb[j].v[i + 2]) * q_scale, to_f32(rb[j].v[i + 3]) * q_scale);
+                if (MODE == LM_GLA) {
+                    float4 a = make_float4(rz[j].v[i], rz[j].v[i + 1], rz[j].v[i + 2], rz[j].v[i + 3]);
+                    if (!gates_are_decays) {
+                        a.x = expf(lm_logsigmoid(a.x) * gate_param);
+                        a.y = expf(lm_logsigmoid(a.y) * gate_param);
+                        a.z = expf(lm_logsigmoid(a.z) * gate_param);
+                        a.w = expf(lm_logsigmoid(a.w) * gate_param);
+                    }
+                    da[i / 4] = a;
+                }
+            }
         }
 #pragma unroll
         for (int e = 0; e < VPT; ++e)
@@ -165,47 +217,67 @@ linear_memory_kernel(const T* __restrict__ qkv, long long qkv_stride, int q_off,
         }
         __syncthreads();
         if (first + TC < qlen) fetch(first + TC);           // in flight while these steps run
-#pragma unroll 2
-        for (int tt = 0; tt < count; ++tt) {
-            const float4* k4 = reinterpret_cast<const float4*>(sk + tt * RPP + sl * Sh::LANE);
-            const float4* q4 = reinterpret_cast<const float4*>(sq + tt * RPP + sl * Sh::LANE);
-            const float4* a4 = reinterpret_cast<const float4*>(sa + (MODE == LM_GLA ? tt * RPP + sl * Sh::LANE : 0));
-            const float vv = is_n ? 1.f : sv[tt * CB + (lc < CB ? lc : 0)];
-            float dot0 = 0.f, dot1 = 0.f;
-            if (MODE == LM_MLSTM) {
-                const float keep = s_keep[tt], tv = s_take[tt] * vv;
+        // four tokens at a time: their updates follow one another, their sums over the rows travel together, so
+        // that one token's shuffles are in flight beside the next one's arithmetic
+        for (int g0 = 0; g0 < count; g0 += LM_GROUP) {
+            float part[LM_GROUP];
 #pragma unroll
-                for (int r4 = 0; r4 < RT / 4; ++r4) {
-                    const float4 kv = k4[r4], qv = q4[r4];
-                    S[4 * r4] = fmaf(kv.x, tv, keep * S[4 * r4]);
-                    S[4 * r4 + 1] = fmaf(kv.y, tv, keep * S[4 * r4 + 1]);
-                    S[4 * r4 + 2] = fmaf(kv.z, tv, keep * S[4 * r4 + 2]);
-                    S[4 * r4 + 3] = fmaf(kv.w, tv, keep * S[4 * r4 + 3]);
-                    dot0 = fmaf(S[4 * r4], qv.x, dot0);
-                    dot1 = fmaf(S[4 * r4 + 1], qv.y, dot1);
-                    dot0 = fmaf(S[4 * r4 + 2], qv.z, dot0);
-                    dot1 = fmaf(S[4 * r4 + 3], qv.w, dot1);
+            for (int u = 0; u < LM_GROUP; ++u) {
+                const int tt = g0 + u;
+                part[u] = 0.f;
+                if (tt >= count) continue;                  // (the same for the whole block)
+                const float4* k4 = reinterpret_cast<const float4*>(sk + tt * RPP + sl * Sh::LANE);
+                const float4* q4 = reinterpret_cast<const float4*>(sq + tt * RPP + sl * Sh::LANE);
+                const float4* a4 = reinterpret_cast<const float4*>(sa + (MODE == LM_GLA ? tt * RPP + sl * Sh::LANE : 0));
+                const float vv = is_n ? 1.f : sv[tt * CB + (lc < CB ? lc : 0)];
+                float dot0 = 0.f, dot1 = 0.f;
+                if (MODE == LM_MLSTM) {
+                    const float keep = s_keep[tt], tv = s_take[tt] * vv;
+#pragma unroll
+                    for (int r4 = 0; r4 < RT / 4; ++r4) {
+                        const float4 kv = k4[r4], qv = q4[r4];
+                        S[4 * r4] = fmaf(kv.x, tv, keep * S[4 * r4]);
+                        S[4 * r4 + 1] = fmaf(kv.y, tv, keep * S[4 * r4 + 1]);
+                        S[4 * r4 + 2] = fmaf(kv.z, tv, keep * S[4 * r4 + 2]);
+                        S[4 * r4 + 3] = fmaf(kv.w, tv, keep * S[4 * r4 + 3]);
+                        dot0 = fmaf(S[4 * r4], qv.x, dot0);
+                        dot1 = fmaf(S[4 * r4 + 1], qv.y, dot1);
+                        dot0 = fmaf(S[4 * r4 + 2], qv.z, dot0);
+                        dot1 = fmaf(S[4 * r4 + 3], qv.w, dot1);
+                    }
+                } else {
+#pragma unroll
+                    for (int r4 = 0; r4 < RT / 4; ++r4) {
+                        const float4 kv = k4[r4], qv = q4[r4], av = a4[r4];
+                        S[4 * r4] = fmaf(kv.x, vv, av.x * S[4 * r4]);
+                        S[4 * r4 + 1] = fmaf(kv.y, vv, av.y * S[4 * r4 + 1]);
+                        S[4 * r4 + 2] = fmaf(kv.z, vv, av.z * S[4 * r4 + 2]);
+                        S[4 * r4 + 3] = fmaf(kv.w, vv, av.w * S[4 * r4 + 3]);
+                        dot0 = fmaf(S[4 * r4], qv.x, dot0);
+                        dot1 = fmaf(S[4 * r4 + 1], qv.y, dot1);
+                        dot0 = fmaf(S[4 * r4 + 2], qv.z, dot0);
+                        dot1 = fmaf(S[4 * r4 + 3], qv.w, dot1);
+                    }
                 }
-            } else {
+                part[u] = dot0 + dot1;
+            }
 #pragma unroll
-                for (int r4 = 0; r4 < RT / 4; ++r4) {
-                    const float4 kv = k4[r4], qv = q4[r4], av = a4[r4];
-                    S[4 * r4] = fmaf(kv.x, vv, av.x * S[4 * r4]);
-                    S[4 * r4 + 1] = fmaf(kv.y, vv, av.y * S[4 * r4 + 1]);
-                    S[4 * r4 + 2] = fmaf(kv.z, vv, av.z * S[4 * r4 + 2]);
-                    S[4 * r4 + 3] = fmaf(kv.w, vv, av.w * S[4 * r4 + 3]);
-                    dot0 = fmaf(S[4 * r4], qv.x, dot0);
-                    dot1 = fmaf(S[4 * r4 + 1], qv.y, dot1);
-                    dot0 = fmaf(S[4 * r4 + 2], qv.z, dot0);
-                    dot1 = fmaf(S[4 * r4 + 3], qv.w, dot1);
+            for (int o = LPC >> 1; o > 0; o >>= 1) {
+#pragma unroll
+                for (int u = 0; u < LM_GROUP; ++u) part[u] += __shfl_xor_sync(0xffffffffu, part[u], o);
+            }
+            if (MODE == LM_MLSTM) {
+#pragma unroll
+                for (int u = 0; u < LM_GROUP; ++u) {
+                    const float nq = __shfl_sync(0xffffffffu, part[u], 0);    // the first group's sum is n . q
+                    part[u] = part[u] / (fmaxf(fabsf(nq), s_floor[min(g0 + u, TC - 1)]) + floor_eps);
                 }
             }
-            float o = lm_lanes_sum<LPC>(dot0 + dot1);
-            if (MODE == LM_MLSTM) {
-                const float nq = __shfl_sync(0xffffffffu, o, 0);         // the first group's sum is n . q
-                o = o / (fmaxf(fabsf(nq), s_floor[tt]) + floor_eps);
+            if (sl == 0 && col_ok) {
+#pragma unroll
+                for (int u = 0; u < LM_GROUP; ++u)
+                    if (g0 + u < count) out[((size_t)(t0 + first + g0 + u) * nh + h) * cols + col] = part[u];
             }
-            if (sl == 0 && col_ok) out[((size_t)(t0 + first + tt) * nh + h) * cols + col] = o;
         }
     }
     pdl_trigger();                                          // (the next kernel is let go when the walk is over)
@@ -221,45 +293,87 @@ linear_memory_kernel(const T* __restrict__ qkv, long long qkv_stride, int q_off,
     if (MODE == LM_MLSTM && blockIdx.x == 0 && threadIdx.x == 0) *m_glob = m_run;
 }
 
-// (RT, LPC) by the number of rows: 8 x 4 up to 32, 16 x 8 up to 128, 16 x 16 up to 256
-#define LM_DISPATCH(ROWS, CALL)                                     \
+// alpha = sigmoid(z)^p = exp(p logsigmoid(z)) over [n, width] rows, in place: once per element for a step with long
+// portions, where every block of a head would otherwise work out the head's decays again
+__global__ void __launch_bounds__(256)
+decay_from_logits_kernel(float* __restrict__ z, long long stride, int width, long long total, float p) {
+    pdl_wait();
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        float* e = z + (i / width) * stride + (i % width);
+        *e = expf(lm_logsigmoid(*e) * p);
+    }
+    pdl_trigger();
+}
+
+// (RT, LPC) by the number of rows: 8 x 4 up to 32, 8 x 8 up to 64, 16 x 8 up to 128, 16 x 16 up to 256.  Gated
+// linear attention of 65 to 128 rows takes 8 x 16 instead while the grid would leave multiprocessors without a block
+// (`fine`): twice the threads share a column.  (The matrix memory gives a column group of every warp to n, so a
+// finer split would spend half of its lanes there.)
+#define LM_DISPATCH(ROWS, FINE, CALL)                               \
     do {                                                            \
         if ((ROWS) <= 32) { CALL(8, 4); }                           \
+        else if ((ROWS) <= 64) { CALL(8, 8); }                      \
+        else if ((ROWS) <= 128 && (FINE)) { CALL(8, 16); }          \
         else if ((ROWS) <= 128) { CALL(16, 8); }                    \
         else { CALL(16, 16); }                                      \
     } while (0)
 
-static inline int lm_lpc(int rows) { return rows <= 32 ? 4 : (rows <= 128 ? 8 : 16); }
+static inline int lm_lpc(int rows, bool fine) { return rows <= 32 ? 4 : (rows <= 64 ? 8 : (rows <= 128 ? (fine ? 16 : 8) : 16)); }
 
 static int lm_launch(int mode, const void* qkv, long long qkv_stride, int q_off, int k_off, int v_off, int dtype,
-                     const float* gates, long long gates_stride, const float* gate_bias, float gate_param, float q_scale,
+                     float* gates, long long gates_stride, const float* gate_bias, float gate_param, float q_scale,
                      float floor_eps, float* state, long long slot_stride, const int* state_slots, const int* cu_q,
-                     const int* positions, float* out, int num_seqs, int nh, int rows, int cols, int num_slots, int max_q,
-                     int* status, cudaStream_t stream, const char* what) {
+                     const int* positions, float* out, int total_rows, int num_seqs, int nh, int rows, int cols, int num_slots,
+                     int max_q, int* status, cudaStream_t stream, const char* what) {
     if (num_seqs <= 0) return 0;
     if (nh <= 0 || rows <= 0 || rows > 256 || cols <= 0)
         return fail(-1, "%s: %d heads, state %d x %d (rows up to 256)", what, nh, rows, cols);
     if (dtype != VAPI_F32 && dtype != VAPI_BF16) return fail(-2, "%s: unsupported dtype %d", what, dtype);
-    const int g = 32 / lm_lpc(rows);
+    static int sms = 0;
+    if (!sms) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    }
+    const int wide = (32 / lm_lpc(rows, false)) * (LM_THREADS / 32);          // columns of a block of the ordinary split
+    const bool fine = mode == LM_GLA && rows > 64 && rows <= 128 &&
+                      (long long)((cols + wide - 1) / wide) * nh * num_seqs < 2LL * sms;
+    const int g = 32 / lm_lpc(rows, fine);
     const int cb = (mode == LM_MLSTM ? g - 1 : g) * (LM_THREADS / 32);
     dim3 grid((cols + cb - 1) / cb, nh, num_seqs);
     if (grid.y > 65535 || grid.z > 65535) return fail(-1, "%s: %d heads x %d sequences are too many", what, nh, num_seqs);
     const bool early = max_q < 16;                         // decode steps may start beside the kernel before; long walks may not
     cudaError_t e = cudaSuccess;
+    // 16-byte loads of the row vectors: every piece of 8 (4 up to 32 rows) starts on its boundary
+    const int ch = rows <= 32 ? 4 : 8;
+    const size_t esz = dtype == VAPI_F32 ? 4 : 2;
+    int wide_loads = rows % ch == 0 && q_off % ch == 0 && k_off % ch == 0 && qkv_stride % ch == 0 &&
+                     (size_t)qkv % (ch * esz > 16 ? 16 : ch * esz) == 0;
+    if (mode == LM_GLA) wide_loads = wide_loads && gates_stride % ch == 0 && (size_t)gates % 16 == 0;
+    int gates_are_decays = 0;
+    if (mode == LM_GLA && !early) {
+        const long long total = (long long)total_rows * nh * rows;
+        const int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
+        e = launch_if(false, decay_from_logits_kernel, dim3(blocks > 0 ? blocks : 1), 256, 0, stream, gates, gates_stride,
+                      nh * rows, total, gate_param);
+        if (e != cudaSuccess) return check_launch(what, e);
+        gates_are_decays = 1;
+    }
 #define LM_CALL_MODE(RT, LPC, M)                                                                                           \
     if (dtype == VAPI_F32)                                                                                                 \
         e = launch_if(early, linear_memory_kernel<float, RT, LPC, M>, grid, LM_THREADS, 0, stream, (const float*)qkv,      \
                       qkv_stride, q_off, k_off, v_off, gates, gates_stride, gate_bias, gate_param, q_scale, floor_eps,     \
-                      state, slot_stride, state_slots, cu_q, positions, out, nh, rows, cols, num_slots, status);           \
+                      state, slot_stride, state_slots, cu_q, positions, out, nh, rows, cols, num_slots, wide_loads,        \
+                      gates_are_decays, status);                                                                           \
     else                                                                                                                   \
         e = launch_if(early, linear_memory_kernel<__nv_bfloat16, RT, LPC, M>, grid, LM_THREADS, 0, stream,                 \
                       (const __nv_bfloat16*)qkv, qkv_stride, q_off, k_off, v_off, gates, gates_stride, gate_bias,          \
                       gate_param, q_scale, floor_eps, state, slot_stride, state_slots, cu_q, positions, out, nh, rows,     \
-                      cols, num_slots, status)
+                      cols, num_slots, wide_loads, gates_are_decays, status)
 #define LM_CALL_A(RT, LPC) LM_CALL_MODE(RT, LPC, LM_MLSTM)
 #define LM_CALL_B(RT, LPC) LM_CALL_MODE(RT, LPC, LM_GLA)
-    if (mode == LM_MLSTM) LM_DISPATCH(rows, LM_CALL_A);
-    else LM_DISPATCH(rows, LM_CALL_B);
+    if (mode == LM_MLSTM) LM_DISPATCH(rows, false, LM_CALL_A);
+    else LM_DISPATCH(rows, fine, LM_CALL_B);
 #undef LM_CALL_A
 #undef LM_CALL_B
 #undef LM_CALL_MODE
@@ -275,20 +389,21 @@ VAPI_EXPORT int vapi_matrix_memory(const void* qkv, long long qkv_stride, int q_
                                    const int* state_slots, const int* cu_q, const int* positions, float* out, int num_seqs,
                                    int nh, int rows, int cols, int num_slots, int max_q, int* status, cudaStream_t stream) {
     if (!(cap > 0.f)) return fail(-1, "matrix_memory: the gates' cap must be positive");
-    return lm_launch(LM_MLSTM, qkv, qkv_stride, q_off, k_off, v_off, dtype, gates, gates_stride, gate_bias, cap, q_scale,
-                     floor_eps, state, slot_stride, state_slots, cu_q, positions, out, num_seqs, nh, rows, cols, num_slots,
-                     max_q, status, stream, "matrix_memory");
+    return lm_launch(LM_MLSTM, qkv, qkv_stride, q_off, k_off, v_off, dtype, const_cast<float*>(gates), gates_stride, gate_bias,
+                     cap, q_scale, floor_eps, state, slot_stride, state_slots, cu_q, positions, out, 0, num_seqs, nh, rows, cols,
+                     num_slots, max_q, status, stream, "matrix_memory");
 }
 
-// As above without gates' scalars: decay_logits [n, *] float holds z [nh, rows] per token; alpha = sigmoid(z)^inv_tau.
+// As above without gates' scalars: decay_logits [num_tokens, *] float holds z [nh, rows] per token; alpha = sigmoid(z)^inv_tau.
+// A step with portions of 16 tokens or more turns z into alpha in place first (decay_logits is scratch then).
 // state: S [nh, rows, cols] per slot.
 VAPI_EXPORT int vapi_gated_linear_attention(const void* qkv, long long qkv_stride, int q_off, int k_off, int v_off, int dtype,
-                                            const float* decay_logits, long long decay_stride, float inv_tau, float q_scale,
+                                            float* decay_logits, long long decay_stride, float inv_tau, float q_scale,
                                             float* state, long long slot_stride, const int* state_slots, const int* cu_q,
-                                            const int* positions, float* out, int num_seqs, int nh, int rows, int cols,
-                                            int num_slots, int max_q, int* status, cudaStream_t stream) {
+                                            const int* positions, float* out, int num_tokens, int num_seqs, int nh, int rows,
+                                            int cols, int num_slots, int max_q, int* status, cudaStream_t stream) {
     return lm_launch(LM_GLA, qkv, qkv_stride, q_off, k_off, v_off, dtype, decay_logits, decay_stride, nullptr, inv_tau,
-                     q_scale, 0.f, state, slot_stride, state_slots, cu_q, positions, out, num_seqs, nh, rows, cols,
+                     q_scale, 0.f, state, slot_stride, state_slots, cu_q, positions, out, num_tokens, num_seqs, nh, rows, cols,
                      num_slots, max_q, status, stream, "gated_linear_attention");
 }
 

@@ -1624,7 +1624,9 @@ def gated_linear_attention(qkv: torch.Tensor, decay_logits: torch.Tensor, tau: f
     """Gated linear attention over every sequence of the step.  ``qkv`` as for :func:`matrix_memory`;
     ``decay_logits`` [n, nh*dk] float32 (unit inner stride) holds z, and key channel r of a head decays by
     ``alpha = sigmoid(z)^(1/tau)``: ``S <- diag(alpha) S + k v^T; o = S^T (q_scale q)``.  ``state``
-    [slots, >= nh*dk*dv] float32 carries S [nh, dk, dv].  Returns o [n, nh*dv] float32."""
+    [slots, >= nh*dk*dv] float32 carries S [nh, dk, dv].  Returns o [n, nh*dv] float32.  ``decay_logits`` is scratch:
+    a step with portions of 16 tokens or more (``max_q``) leaves the decays in it, worked out once per element by a
+    kernel of their own instead of by every block of a head."""
     _linear_memory_args(qkv, nh, dk, dv, state, nh * dk * dv, state_slots, cu_q, positions)
     _cuda(decay_logits)
     n = qkv.shape[0]
@@ -1637,6 +1639,6 @@ def gated_linear_attention(qkv: torch.Tensor, decay_logits: torch.Tensor, tau: f
     _check(lib, lib.vapi_gated_linear_attention(
         _p(qkv), ctypes.c_longlong(qkv.stride(0)), 0, nh * dk, 2 * nh * dk, _dt(qkv), _p(decay_logits),
         ctypes.c_longlong(decay_logits.stride(0)), ctypes.c_float(1.0 / tau), ctypes.c_float(q_scale), _p(state),
-        ctypes.c_longlong(state.stride(0)), _p(state_slots), _p(cu_q), _p(positions), _p(out), cu_q.numel() - 1, nh, dk, dv,
-        state.shape[0], int(min(max_q, 1 << 30)), _p(status), _stream()))
+        ctypes.c_longlong(state.stride(0)), _p(state_slots), _p(cu_q), _p(positions), _p(out), n, cu_q.numel() - 1, nh, dk, dv,
+        state.shape[0], int(min(max_q, 1 << 30)), _p(status), _stream()), 2 if max_q >= 16 else 1)
     return out

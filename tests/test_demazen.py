@@ -409,7 +409,9 @@ def test_memory_kernels_continue_from_their_state_and_start_fresh_at_position_ze
     lens, starts, slots = [1, 9, 2, 70, 1], [0, 5, 0, 1, 33], [3, 0, 2, 1, 4]
     cu, pos, sl = _step_meta(lens, starts, slots, "cuda")
     n = sum(lens)
-    for nh, dk, dv in ((3, 20, 12), (2, 32, 48), (1, 72, 40), (2, 136, 8), (1, 200, 28), (5, 12, 4), (1, 1, 1), (2, 64, 64)):
+    # (65 to 128 rows: few blocks take the finer split of the rows, many the ordinary one)
+    for nh, dk, dv in ((3, 20, 12), (2, 32, 48), (1, 72, 40), (1, 100, 24), (8, 128, 128), (2, 136, 8), (1, 200, 28), (5, 12, 4), (1, 1, 1),
+                       (2, 64, 64)):
         cols = 2 * nh * dk + nh * dv
         qkv = torch.randn((n, cols + 9), generator=g).to(dtype)
         pre = torch.randn((n, 2 * nh), generator=g) * 3.0

@@ -305,10 +305,11 @@ decay_from_logits_kernel(float* __restrict__ z, long long stride, int width, lon
     pdl_trigger();
 }
 
-// (RT, LPC) by the number of rows: 8 x 4 up to 32, 8 x 8 up to 64, 16 x 8 up to 128, 16 x 16 up to 256.  Gated
-// linear attention of 65 to 128 rows takes 8 x 16 instead while the grid would leave multiprocessors without a block
-// (`fine`): twice the threads share a column.  (The matrix memory gives a column group of every warp to n, so a
-// finer split would spend half of its lanes there.)
+// (RT, LPC) by the number of rows: 8 x 4 up to 32, 8 x 8 up to 64, 16 x 8 up to 128, 16 x 16 up to 256.  A state of
+// 65 to 128 rows takes 8 x 16 instead while the grid would leave schedulers without a warp (`fine`): twice the
+// threads share a column and a token's chain of updates is half as long.  (The matrix memory gives a column group of
+// every warp to n, so its finer split spends half of its lanes there; with one prompt in the step that still
+// beats one warp a scheduler walking twice the rows.)
 #define LM_DISPATCH(ROWS, FINE, CALL)                               \
     do {                                                            \
         if ((ROWS) <= 32) { CALL(8, 4); }                           \
@@ -335,9 +336,9 @@ static int lm_launch(int mode, const void* qkv, long long qkv_stride, int q_off,
         cudaGetDevice(&dev);
         if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
     }
-    const int wide = (32 / lm_lpc(rows, false)) * (LM_THREADS / 32);          // columns of a block of the ordinary split
-    const bool fine = mode == LM_GLA && rows > 64 && rows <= 128 &&
-                      (long long)((cols + wide - 1) / wide) * nh * num_seqs < 2LL * sms;
+    const int g_wide = 32 / lm_lpc(rows, false);                               // column groups a warp of the ordinary split
+    const int wide = (mode == LM_MLSTM ? g_wide - 1 : g_wide) * (LM_THREADS / 32);
+    const bool fine = rows > 64 && rows <= 128 && (long long)((cols + wide - 1) / wide) * nh * num_seqs < 2LL * sms;
     const int g = 32 / lm_lpc(rows, fine);
     const int cb = (mode == LM_MLSTM ? g - 1 : g) * (LM_THREADS / 32);
     dim3 grid((cols + cb - 1) / cb, nh, num_seqs);
@@ -372,7 +373,7 @@ static int lm_launch(int mode, const void* qkv, long long qkv_stride, int q_off,
                       cols, num_slots, wide_loads, gates_are_decays, status)
 #define LM_CALL_A(RT, LPC) LM_CALL_MODE(RT, LPC, LM_MLSTM)
 #define LM_CALL_B(RT, LPC) LM_CALL_MODE(RT, LPC, LM_GLA)
-    if (mode == LM_MLSTM) LM_DISPATCH(rows, false, LM_CALL_A);
+    if (mode == LM_MLSTM) LM_DISPATCH(rows, fine, LM_CALL_A);
     else LM_DISPATCH(rows, fine, LM_CALL_B);
 #undef LM_CALL_A
 #undef LM_CALL_B

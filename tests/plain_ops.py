@@ -631,7 +631,7 @@ def matrix_memory(qkv, gates, gate_bias, cap, state, state_slots, cu_q, position
         if r1 == r0:
             continue
         slot = int(state_slots[s])
-        S = state[slot, :nS].view(nh, dk, dv).clone()
+        S = state[slot, :nS].view(nh, dv, dk).transpose(1, 2).clone()          # the slot holds S column by column
         nv = state[slot, nS:nS + nn].view(nh, dk).clone()
         m = state[slot, nS + nn:nS + nn + nh].clone()
         if int(positions[r0]) == 0:
@@ -652,7 +652,7 @@ def matrix_memory(qkv, gates, gate_bias, cap, state, state_slots, cu_q, position
                 m[h] = new
                 den = torch.maximum((nv[h] @ qv).abs(), torch.exp(-new)) + floor_eps
                 out[r, h * dv:(h + 1) * dv] = (S[h].t() @ qv) / den
-        state[slot, :nS] = S.reshape(-1)
+        state[slot, :nS] = S.transpose(1, 2).reshape(-1)
         state[slot, nS:nS + nn] = nv.reshape(-1)
         state[slot, nS + nn:nS + nn + nh] = m
     return out
@@ -668,7 +668,7 @@ def gated_linear_attention(qkv, decay_logits, tau, state, state_slots, cu_q, pos
         if r1 == r0:
             continue
         slot = int(state_slots[s])
-        S = state[slot, :nS].view(nh, dk, dv).clone()
+        S = state[slot, :nS].view(nh, dv, dk).transpose(1, 2).clone()          # the slot holds S column by column
         if int(positions[r0]) == 0:
             S.zero_()
         for r in range(r0, r1):
@@ -680,7 +680,7 @@ def gated_linear_attention(qkv, decay_logits, tau, state, state_slots, cu_q, pos
                 vv = row[2 * nh * dk + h * dv:2 * nh * dk + (h + 1) * dv]
                 S[h] = alpha[h][:, None] * S[h] + torch.outer(kv, vv)
                 out[r, h * dv:(h + 1) * dv] = S[h].t() @ qv
-        state[slot, :nS] = S.reshape(-1)
+        state[slot, :nS] = S.transpose(1, 2).reshape(-1)
     return out
 
 

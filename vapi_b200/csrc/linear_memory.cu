@@ -8,7 +8,8 @@
 //       S <- diag(alpha) S + k v^T;   o = S^T q;   alpha = sigmoid(z)^(1/tau) = exp(logsigmoid(z) / tau)
 //
 // q is multiplied by `q_scale` on its way in.  S is [rows, cols] (key size x value size), float, in the
-// request's state slot; the matrix memory keeps n [heads, rows] and m [heads] behind all heads' S.  Memory is
+// request's state slot, stored column by column ([heads, cols, rows]: a column's rows side by side); the matrix
+// memory keeps n [heads, rows] and m [heads] behind all heads' S.  Memory is
 // never cleared: a sequence whose first token of the step sits at position 0 starts from zeros (m from 0)
 // whatever its slot holds.  Gates, decays, their logarithms and exponentials, n, m and S are float whatever T is;
 // the gates' pre-activations come in as float.
@@ -108,14 +109,20 @@ linear_memory_kernel(const T* __restrict__ qkv, long long qkv_stride, int q_off,
     pdl_wait();
     // the state is asked for before it is known whether the sequence starts here, so that a decode step's loads
     // (the slot's state and the position) are in flight together; a fresh sequence drops what came
+    // (a column's rows lie side by side in the slot, so a lane's rows are one run of floats and a warp's loads whole lines)
     float S[RT];
+    float* S_mine = is_n ? n_glob + r0 : S_glob + (size_t)(col_ok ? col : 0) * rows + r0;
+    const bool mine = is_n || col_ok;
+    if (wide_loads & 2) {
 #pragma unroll
-    for (int j = 0; j < RT; ++j) {
-        S[j] = 0.f;
-        if (r0 + j < rows) {
-            if (is_n) S[j] = n_glob[r0 + j];
-            else if (col_ok) S[j] = S_glob[(size_t)(r0 + j) * cols + col];
+        for (int j = 0; j < RT; j += 4) {
+            float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (mine && r0 + j < rows) x = *reinterpret_cast<const float4*>(S_mine + j);       // (rows come in fours)
+            S[j] = x.x, S[j + 1] = x.y, S[j + 2] = x.z, S[j + 3] = x.w;
         }
+    } else {
+#pragma unroll
+        for (int j = 0; j < RT; ++j) S[j] = (mine && r0 + j < rows) ? S_mine[j] : 0.f;
     }
     float m_run = MODE == LM_MLSTM ? *m_glob : 0.f;                      // (every lane of the first warp carries it)
     const bool fresh = positions[t0] == 0;
@@ -139,7 +146,7 @@ linear_memory_kernel(const T* __restrict__ qkv, long long qkv_stride, int q_off,
             const int tt = idx / RP, r = idx - tt * RP;
             const T* row = qkv + (size_t)(t0 + first + tt) * qkv_stride + h * rows + r;
             const float* zrow = gates + (size_t)(t0 + first + tt) * gates_stride + h * rows + r;
-            if (wide_loads && tt < count && r < rows) {          // (rows is a multiple of CH then: the piece is whole)
+            if ((wide_loads & 1) && tt < count && r < rows) {          // (rows is a multiple of CH then: the piece is whole)
                 ra[j].raw = *reinterpret_cast<const LmRaw<CH * (int)sizeof(T)>*>(row + k_off);
                 rb[j].raw = *reinterpret_cast<const LmRaw<CH * (int)sizeof(T)>*>(row + q_off);
                 if (MODE == LM_GLA) rz[j].raw = *reinterpret_cast<const LmRaw<CH * 4>*>(zrow);
@@ -281,14 +288,15 @@ linear_memory_kernel(const T* __restrict__ qkv, long long qkv_stride, int q_off,
         }
     }
     pdl_trigger();                                          // (the next kernel is let go when the walk is over)
+    const bool put = is_n ? (blockIdx.x == 0 && warp == 0) : col_ok;
+    if (wide_loads & 2) {
 #pragma unroll
-    for (int j = 0; j < RT; ++j) {
-        if (r0 + j >= rows) continue;
-        if (is_n) {
-            if (blockIdx.x == 0 && warp == 0) n_glob[r0 + j] = S[j];
-        } else if (col_ok) {
-            S_glob[(size_t)(r0 + j) * cols + col] = S[j];
-        }
+        for (int j = 0; j < RT; j += 4)
+            if (put && r0 + j < rows) *reinterpret_cast<float4*>(S_mine + j) = make_float4(S[j], S[j + 1], S[j + 2], S[j + 3]);
+    } else {
+#pragma unroll
+        for (int j = 0; j < RT; ++j)
+            if (put && r0 + j < rows) S_mine[j] = S[j];
     }
     if (MODE == LM_MLSTM && blockIdx.x == 0 && threadIdx.x == 0) *m_glob = m_run;
 }
@@ -351,6 +359,8 @@ static int lm_launch(int mode, const void* qkv, long long qkv_stride, int q_off,
     int wide_loads = rows % ch == 0 && q_off % ch == 0 && k_off % ch == 0 && qkv_stride % ch == 0 &&
                      (size_t)qkv % (ch * esz > 16 ? 16 : ch * esz) == 0;
     if (mode == LM_GLA) wide_loads = wide_loads && gates_stride % ch == 0 && (size_t)gates % 16 == 0;
+    // 16-byte accesses of the state: a lane's run of rows starts on a boundary (n and m lie behind whole columns)
+    if (rows % 4 == 0 && slot_stride % 4 == 0 && (size_t)state % 16 == 0) wide_loads |= 2;
     int gates_are_decays = 0;
     if (mode == LM_GLA && !early) {
         const long long total = (long long)total_rows * nh * rows;
@@ -383,7 +393,7 @@ static int lm_launch(int mode, const void* qkv, long long qkv_stride, int q_off,
 
 // qkv [n, *]: q heads [nh, rows] at q_off, k heads [nh, rows] at k_off, v heads [nh, cols] at v_off of a row of
 // `qkv_stride` elements.  gates [n, *] float: the input gates' pre-activations [nh], then the forget gates' [nh];
-// gate_bias [2 * nh] likewise (may be null).  state: S [nh, rows, cols], n [nh, rows], m [nh] per slot.  out [n, nh * cols] float.
+// gate_bias [2 * nh] likewise (may be null).  state: S [nh, cols, rows] (column by column), n [nh, rows], m [nh] per slot.  out [n, nh * cols] float.
 VAPI_EXPORT int vapi_matrix_memory(const void* qkv, long long qkv_stride, int q_off, int k_off, int v_off, int dtype,
                                    const float* gates, long long gates_stride, const float* gate_bias, float cap,
                                    float q_scale, float floor_eps, float* state, long long slot_stride,
@@ -397,7 +407,7 @@ VAPI_EXPORT int vapi_matrix_memory(const void* qkv, long long qkv_stride, int q_
 
 // As above without gates' scalars: decay_logits [num_tokens, *] float holds z [nh, rows] per token; alpha = sigmoid(z)^inv_tau.
 // A step with portions of 16 tokens or more turns z into alpha in place first (decay_logits is scratch then).
-// state: S [nh, rows, cols] per slot.
+// state: S [nh, cols, rows] (column by column) per slot.
 VAPI_EXPORT int vapi_gated_linear_attention(const void* qkv, long long qkv_stride, int q_off, int k_off, int v_off, int dtype,
                                             float* decay_logits, long long decay_stride, float inv_tau, float q_scale,
                                             float* state, long long slot_stride, const int* state_slots, const int* cu_q,

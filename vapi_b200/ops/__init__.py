@@ -1598,7 +1598,8 @@ def matrix_memory(qkv: torch.Tensor, gates: torch.Tensor, gate_bias: Optional[to
     ``lf = logsigmoid(cap tanh(a_f / cap))`` and a running maximum m that starts at 0:
     ``m' = max(lf + m, li); S <- exp(lf + m - m') S + exp(li - m') k v^T``, n likewise with k alone, and
     ``o = S^T (q_scale q) / (max(|n . q_scale q|, exp(-m')) + floor_eps)``.  ``state`` [slots, >= nh*dk*dv + nh*dk + nh]
-    float32 carries S [nh, dk, dv], n [nh, dk] and m [nh].  Returns o [n, nh*dv] float32."""
+    float32 carries S [nh, dv, dk] (column by column: a value column's key rows side by side), n [nh, dk] and m [nh].
+    Returns o [n, nh*dv] float32."""
     need = nh * dk * dv + nh * dk + nh
     _linear_memory_args(qkv, nh, dk, dv, state, need, state_slots, cu_q, positions)
     _cuda(gates, gate_bias)
@@ -1624,7 +1625,7 @@ def gated_linear_attention(qkv: torch.Tensor, decay_logits: torch.Tensor, tau: f
     """Gated linear attention over every sequence of the step.  ``qkv`` as for :func:`matrix_memory`;
     ``decay_logits`` [n, nh*dk] float32 (unit inner stride) holds z, and key channel r of a head decays by
     ``alpha = sigmoid(z)^(1/tau)``: ``S <- diag(alpha) S + k v^T; o = S^T (q_scale q)``.  ``state``
-    [slots, >= nh*dk*dv] float32 carries S [nh, dk, dv].  Returns o [n, nh*dv] float32.  ``decay_logits`` is scratch:
+    [slots, >= nh*dk*dv] float32 carries S [nh, dv, dk] (column by column).  Returns o [n, nh*dv] float32.  ``decay_logits`` is scratch:
     a step with portions of 16 tokens or more (``max_q``) leaves the decays in it, worked out once per element by a
     kernel of their own instead of by every block of a head."""
     _linear_memory_args(qkv, nh, dk, dv, state, nh * dk * dv, state_slots, cu_q, positions)

@@ -278,11 +278,17 @@ def apply_penalties(logits, rows, toks, counts, rep, freq, pres):
 
 
 # ---- blocks with norms on both sides, scaled rotary tables, general attention, recurrent mixers -----
-def postnorm_add_rmsnorm(x, y, post_weight, post_eps, mult, weight, eps, out_dtype, rows=None, copy=False):
-    """x += mult * rms(y) * post_weight;  out = rms(x) * weight, or x itself with `copy` (for `rows` only, x untouched)."""
+def postnorm_add_rmsnorm(x, y, post_weight, post_eps, mult, weight, eps, out_dtype, rows=None, copy=False, branches=None):
+    """x += mult * rms(y) * post_weight;  out = rms(x) * weight, or x itself with `copy` (for `rows` only, x untouched).
+    branches = (y2, wa, wb, eps_b, scale): scale * (rms(y) * wa + rms(y2) * wb) stands for y."""
     add = None
     if y is not None:
         yf = _f(y)
+        if branches is not None:
+            y2, wa, wb, eps_b, scale = branches
+            y2f = _f(y2)
+            yf = scale * (yf * torch.rsqrt(yf.pow(2).mean(-1, keepdim=True) + eps_b) * wa
+                          + y2f * torch.rsqrt(y2f.pow(2).mean(-1, keepdim=True) + eps_b) * wb)
         add = mult * (yf * torch.rsqrt(yf.pow(2).mean(-1, keepdim=True) + post_eps) * post_weight)
     if rows is None:
         if add is not None:

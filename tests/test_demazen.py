@@ -436,3 +436,29 @@ def test_memory_kernels_continue_from_their_state_and_start_fresh_at_position_ze
         got = ops.gated_linear_attention(qkv.cuda()[:, :cols], z.cuda(), 3.0, dstate, sl, cu, pos, nh, dk, dv, dk ** -0.5, max_q=max(lens))
         _close(got, want, 2e-4)
         _close(dstate, want_state, 2e-4)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("hidden", [99, 320, 2048, 4100])
+def test_two_raw_branches_ride_on_the_post_norm(hidden, dtype):
+    """``x += rmsnorm(mean of the two branch norms) * w`` in one kernel against its restatement: every row, selected
+    rows (the stream untouched), with a following norm and with the stream's rows handed on as they are."""
+    from vapi_b200 import ops
+    g = torch.Generator().manual_seed(hidden)
+    n = 37
+    x = torch.randn((n, hidden), generator=g)
+    ya, yb = (torch.randn((n, hidden), generator=g) * s for s in (3.0, 0.02))
+    ya, yb = ya.to(dtype), yb.to(dtype)
+    wa, wb, wp, w = (torch.randn(hidden, generator=g) for _ in range(4))
+    rows = torch.tensor([5, 0, 36, 5], dtype=torch.int32)
+    tol = 2e-5 if dtype == torch.float32 else 2e-2
+    for r in (None, rows):
+        for weight, copy in ((w, False), (None, True)):
+            xr, xd = x.clone(), x.clone().cuda()
+            want = plain_ops.postnorm_add_rmsnorm(xr, ya, wp, 1e-5, 0.7, weight, 1e-6, dtype, r, copy=copy, branches=(yb, wa, wb, 1e-4, 0.5))
+            got = ops.postnorm_add_rmsnorm(xd, ya.cuda(), wp.cuda(), 1e-5, 0.7, None if weight is None else weight.cuda(), 1e-6, dtype,
+                                           None if r is None else r.cuda(), copy=copy, branches=(yb.cuda(), wa.cuda(), wb.cuda(), 1e-4, 0.5))
+            _close(got.float(), want.float(), tol)
+            _close(xd, xr, 2e-5)
+            assert (r is None) != torch.equal(xd.cpu(), x), "selected rows leave the stream as it was"

@@ -387,13 +387,18 @@ VAPI_EXPORT int vapi_swiglu(const void* g, void* out, int dtype, int rows, int f
 // `w` null: no norm follows; with `out` the row itself is handed on in T (a sublayer that reads the stream as
 // it is), without it only the stream is updated.  With `rows` the output has one row per entry and x is left
 // untouched.
+// With `y2` the sublayer was two mixers side by side whose outputs y and y2 are still raw: y stands for
+//   scale_b * (y * rsqrt(mean(y^2) + eps_b) * wa + y2 * rsqrt(mean(y2^2) + eps_b) * wb)
+// which is formed here, in float, before anything else.
 // One block per row; every sum is float.
 template <typename T>
 __global__ void postnorm_add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ y,
                                             const float* __restrict__ w_post, float eps_post, float mult,
                                             const float* __restrict__ w, float eps,
                                             const int* __restrict__ rows, T* __restrict__ out,
-                                            int n_out, int hidden, int write_x) {
+                                            int n_out, int hidden, int write_x, const T* __restrict__ y2,
+                                            const float* __restrict__ wa, const float* __restrict__ wb, float eps_b,
+                                            float scale_b) {
     __shared__ float red[33];
     const int j = blockIdx.x;
     pdl_trigger();
@@ -402,16 +407,33 @@ __global__ void postnorm_add_rmsnorm_kernel(float* __restrict__ x, const T* __re
     const int row = rows ? rows[j] : j;
     float* xr = x + (size_t)row * hidden;
     const T* yr = y ? y + (size_t)row * hidden : nullptr;
+    const T* y2r = (y && y2) ? y2 + (size_t)row * hidden : nullptr;
+    float inv_a = 0.f, inv_b = 0.f;
+    if (y2r) {
+        float sa = 0.f, sb = 0.f;
+        for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+            const float a = to_f32(yr[c]), b = to_f32(y2r[c]);
+            sa += a * a;
+            sb += b * b;
+        }
+        sa = block_sum(sa, red);
+        sb = block_sum(sb, red);
+        inv_a = rsqrtf(sa / (float)hidden + eps_b);
+        inv_b = rsqrtf(sb / (float)hidden + eps_b);
+    }
+    auto yval = [&](int c) {
+        return y2r ? scale_b * (to_f32(yr[c]) * inv_a * wa[c] + to_f32(y2r[c]) * inv_b * wb[c]) : to_f32(yr[c]);
+    };
     float ssy = 0.f;
     for (int c = threadIdx.x; c < hidden && yr; c += blockDim.x) {
-        const float v = to_f32(yr[c]);
+        const float v = yval(c);
         ssy += v * v;
     }
     if (yr) ssy = block_sum(ssy, red);
     const float inv_y = rsqrtf(ssy / (float)hidden + eps_post);
     float ss = 0.f;
     for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
-        const float v = yr ? xr[c] + mult * (to_f32(yr[c]) * inv_y * w_post[c]) : xr[c];
+        const float v = yr ? xr[c] + mult * (yval(c) * inv_y * w_post[c]) : xr[c];
         if (write_x && yr) xr[c] = v;
         ss += v * v;
     }
@@ -424,7 +446,7 @@ __global__ void postnorm_add_rmsnorm_kernel(float* __restrict__ x, const T* __re
     T* orow = out + (size_t)j * hidden;
     for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
         // each thread reads back what it wrote itself
-        const float v = (write_x || !yr) ? xr[c] : xr[c] + mult * (to_f32(yr[c]) * inv_y * w_post[c]);
+        const float v = (write_x || !yr) ? xr[c] : xr[c] + mult * (yval(c) * inv_y * w_post[c]);
         orow[c] = from_f32<T>(w ? v * inv * w[c] : v);
     }
 }
@@ -437,7 +459,9 @@ __global__ void postnorm_add_rmsnorm_vec_kernel(float* __restrict__ x, const T* 
                                                 const float* __restrict__ w_post, float eps_post, float mult,
                                                 const float* __restrict__ w, float eps,
                                                 const int* __restrict__ rows, T* __restrict__ out,
-                                                int n_out, int hidden, int write_x) {
+                                                int n_out, int hidden, int write_x, const T* __restrict__ y2,
+                                                const float* __restrict__ wa, const float* __restrict__ wb, float eps_b,
+                                                float scale_b) {
     __shared__ float red[33];
     const int j = blockIdx.x;
     pdl_trigger();
@@ -446,16 +470,48 @@ __global__ void postnorm_add_rmsnorm_vec_kernel(float* __restrict__ x, const T* 
     const int row = rows ? rows[j] : j;
     float* xr = x + (size_t)row * hidden;
     const T* yr = y ? y + (size_t)row * hidden : nullptr;
+    const T* y2r = (y && y2) ? y2 + (size_t)row * hidden : nullptr;
     const int h4 = hidden >> 2;
     float4 v[NORM_KMAX];
     float ssy = 0.f;
+    if (y2r) {                                   // two raw branches: their norms and their mean come first
+        float4 u[NORM_KMAX];
+        float sa = 0.f, sb = 0.f;
 #pragma unroll
-    for (int k = 0; k < NORM_KMAX; ++k) {
-        const int c = threadIdx.x + k * blockDim.x;
-        v[k] = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (c < h4 && yr) {
-            v[k] = Pack4<T>::load(yr + 4 * c);
-            ssy += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+        for (int k = 0; k < NORM_KMAX; ++k) {
+            const int c = threadIdx.x + k * blockDim.x;
+            v[k] = u[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (c < h4) {
+                v[k] = Pack4<T>::load(yr + 4 * c);
+                u[k] = Pack4<T>::load(y2r + 4 * c);
+                sa += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+                sb += u[k].x * u[k].x + u[k].y * u[k].y + u[k].z * u[k].z + u[k].w * u[k].w;
+            }
+        }
+        sa = block_sum(sa, red);
+        sb = block_sum(sb, red);
+        const float inv_a = rsqrtf(sa / (float)hidden + eps_b), inv_b = rsqrtf(sb / (float)hidden + eps_b);
+#pragma unroll
+        for (int k = 0; k < NORM_KMAX; ++k) {
+            const int c = threadIdx.x + k * blockDim.x;
+            if (c < h4) {
+                const float4 a4 = Pack4<float>::load(wa + 4 * c), b4 = Pack4<float>::load(wb + 4 * c);
+                v[k].x = scale_b * (v[k].x * inv_a * a4.x + u[k].x * inv_b * b4.x);
+                v[k].y = scale_b * (v[k].y * inv_a * a4.y + u[k].y * inv_b * b4.y);
+                v[k].z = scale_b * (v[k].z * inv_a * a4.z + u[k].z * inv_b * b4.z);
+                v[k].w = scale_b * (v[k].w * inv_a * a4.w + u[k].w * inv_b * b4.w);
+                ssy += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+            }
+        }
+    } else {
+#pragma unroll
+        for (int k = 0; k < NORM_KMAX; ++k) {
+            const int c = threadIdx.x + k * blockDim.x;
+            v[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (c < h4 && yr) {
+                v[k] = Pack4<T>::load(yr + 4 * c);
+                ssy += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+            }
         }
     }
     if (yr) ssy = block_sum(ssy, red);
@@ -502,9 +558,11 @@ __global__ void postnorm_add_rmsnorm_vec_kernel(float* __restrict__ x, const T* 
 
 VAPI_EXPORT int vapi_postnorm_add_rmsnorm(float* x, const void* y, int dtype, const float* w_post, float eps_post,
                                           float mult, const float* w, float eps, const int* rows, void* out,
-                                          int n_out, int hidden, cudaStream_t stream) {
+                                          int n_out, int hidden, const void* y2, const float* wa, const float* wb,
+                                          float eps_b, float scale_b, cudaStream_t stream) {
     if (n_out <= 0) return 0;
     if (hidden <= 0 || (y && !w_post)) return fail(-1, "postnorm_add_rmsnorm: hidden=%d or no weight", hidden);
+    if (y2 && (!y || !wa || !wb)) return fail(-1, "postnorm_add_rmsnorm: two branches come with both outputs and both weights");
     if (!y && !out) return 0;
     if (w && !out) return fail(-1, "postnorm_add_rmsnorm: a following norm needs an output");
     const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
@@ -515,19 +573,21 @@ VAPI_EXPORT int vapi_postnorm_add_rmsnorm(float* x, const void* y, int dtype, co
         if (hidden / 4 <= NORM_KMAX * vt) {
             if (dtype == VAPI_F32)
                 e = launch(postnorm_add_rmsnorm_vec_kernel<float>, n_out, vt, 0, stream, x, (const float*)y, w_post, eps_post,
-                           mult, w, eps, rows, (float*)out, n_out, hidden, write_x);
+                           mult, w, eps, rows, (float*)out, n_out, hidden, write_x, (const float*)y2, wa, wb, eps_b, scale_b);
             else
                 e = launch(postnorm_add_rmsnorm_vec_kernel<__nv_bfloat16>, n_out, vt, 0, stream, x, (const __nv_bfloat16*)y,
-                           w_post, eps_post, mult, w, eps, rows, (__nv_bfloat16*)out, n_out, hidden, write_x);
+                           w_post, eps_post, mult, w, eps, rows, (__nv_bfloat16*)out, n_out, hidden, write_x,
+                           (const __nv_bfloat16*)y2, wa, wb, eps_b, scale_b);
             return check_launch("postnorm_add_rmsnorm", e);
         }
     }
     if (dtype == VAPI_F32)
         e = launch(postnorm_add_rmsnorm_kernel<float>, n_out, threads, 0, stream, x, (const float*)y, w_post, eps_post, mult,
-                   w, eps, rows, (float*)out, n_out, hidden, write_x);
+                   w, eps, rows, (float*)out, n_out, hidden, write_x, (const float*)y2, wa, wb, eps_b, scale_b);
     else if (dtype == VAPI_BF16)
         e = launch(postnorm_add_rmsnorm_kernel<__nv_bfloat16>, n_out, threads, 0, stream, x, (const __nv_bfloat16*)y, w_post,
-                   eps_post, mult, w, eps, rows, (__nv_bfloat16*)out, n_out, hidden, write_x);
+                   eps_post, mult, w, eps, rows, (__nv_bfloat16*)out, n_out, hidden, write_x, (const __nv_bfloat16*)y2, wa, wb,
+                   eps_b, scale_b);
     else
         return fail(-2, "postnorm_add_rmsnorm: unsupported dtype %d", dtype);
     return check_launch("postnorm_add_rmsnorm", e);

@@ -159,7 +159,8 @@ def _block(cfg: DemazenConfig, layer: DemazenLayer) -> SandwichBlock:
                                                "norm": "norm"})
         if ri["rank"] is not None:
             gla.with_rank(ri["rank"])
-        mixer = ParallelMixer(W, [("left.", attn), ("right.", gla)], eps, norm_name="out")
+        # (the two branch norms and their mean ride on the kernel that norms the mixer's output into the stream)
+        mixer = ParallelMixer(W, [("left.", attn), ("right.", gla)], eps, norm_name="out", deferred=True)
     ffn = ffn_norm = ffn_post = None
     if layer.mlp is not None:
         m = dict(layer.mlp)

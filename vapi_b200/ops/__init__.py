@@ -1020,13 +1020,25 @@ def apply_penalties(logits: torch.Tensor, rows: torch.Tensor, toks: torch.Tensor
 # with unlike key and value widths, chunked masks, sinks and head gates; recurrent mixers
 def postnorm_add_rmsnorm(x: torch.Tensor, y: Optional[torch.Tensor], post_weight: Optional[torch.Tensor], post_eps: float,
                          mult: float, weight: Optional[torch.Tensor], eps: float, out_dtype: torch.dtype,
-                         rows: Optional[torch.Tensor] = None, copy: bool = False) -> Optional[torch.Tensor]:
+                         rows: Optional[torch.Tensor] = None, copy: bool = False, branches=None) -> Optional[torch.Tensor]:
     """``x += mult * rmsnorm(y) * post_weight`` on the float32 stream and, with ``weight``,
     ``out = rmsnorm(x) * weight`` in one pass.  With ``rows`` only those rows are produced and
     ``x`` is left untouched.  ``y`` None: nothing is pending.  ``weight`` None: no norm follows; with ``copy`` the
     rows of the stream themselves are returned in ``out_dtype`` (for a sublayer that reads the stream as it is),
-    else only the stream is updated (returns None)."""
+    else only the stream is updated (returns None).  ``branches`` = (y2, weight_a, weight_b, eps, scale): the
+    sublayer was two mixers side by side whose raw outputs are ``y`` and ``y2``, and
+    ``scale * (rmsnorm(y) * weight_a + rmsnorm(y2) * weight_b)`` (float32) stands where ``y`` stands above."""
     _cuda(x, y, post_weight, weight, rows)
+    y2 = wa = wb = None
+    eps_b = scale_b = 0.0
+    if branches is not None:
+        y2, wa, wb, eps_b, scale_b = branches
+        _cuda(y2, wa, wb)
+        _f32(wa, "norm weight")
+        _f32(wb, "norm weight")
+        _contig(y2, "sublayer output")
+        if y is None or y2.shape != y.shape or y2.dtype != y.dtype or wa.numel() != x.shape[-1] or wb.numel() != x.shape[-1]:
+            raise KernelError("two branches come with outputs of one shape and dtype and a weight per column each")
     _f32(x, "residual stream")
     _f32(post_weight, "norm weight")
     _f32(weight, "norm weight")
@@ -1048,7 +1060,8 @@ def postnorm_add_rmsnorm(x: torch.Tensor, y: Optional[torch.Tensor], post_weight
     lib = _lib("elementwise")
     _check(lib, lib.vapi_postnorm_add_rmsnorm(_p(x), _p(y), _DT[out_dtype], _p(post_weight), ctypes.c_float(post_eps),
                                               ctypes.c_float(mult), _p(weight), ctypes.c_float(eps), _p(rows), _p(out),
-                                              n_out, hidden, _stream()))
+                                              n_out, hidden, _p(y2), _p(wa), _p(wb), ctypes.c_float(eps_b),
+                                              ctypes.c_float(scale_b), _stream()))
     return out
 
 

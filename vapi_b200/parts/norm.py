@@ -9,6 +9,17 @@ from .. import ops
 from .base import Norm, NormedStream, PostNormed, TensorSpec, register_norm
 
 
+def _raw_branches(y):
+    """A sublayer's output as the post-norm kernel takes it.  Mixers side by side may hand on their raw outputs
+    (``outs``, ``weights``, ``eps``, ``scale``): two of them ride on the kernel that norms the sublayer into the
+    stream, any other number is normed and averaged by a kernel of its own first."""
+    if not hasattr(y, "outs"):
+        return y, None
+    if len(y.outs) == 2:
+        return y.outs[0], (y.outs[1], y.weights[0], y.weights[1], y.eps, y.scale)
+    return y.tensor(), None
+
+
 class RMSNorm(Norm):
     """``y = x * rsqrt(mean(x^2) + eps) * w``: the weight multiplies as it is (no ``1 + w``)
     (crates/vapi-backend-candle/src/models/lfm2.rs:626-628).  Mean, rsqrt and the residual
@@ -29,8 +40,9 @@ class RMSNorm(Norm):
 
     def apply(self, x, delta, dtype, rows=None):
         if isinstance(delta, PostNormed):
-            return ops.postnorm_add_rmsnorm(x, delta.y, delta.weight, delta.eps, delta.mult, self.weight, self.eps,
-                                            dtype, rows)
+            y, branches = _raw_branches(delta.y)
+            return ops.postnorm_add_rmsnorm(x, y, delta.weight, delta.eps, delta.mult, self.weight, self.eps,
+                                            dtype, rows, branches=branches)
         return ops.add_rmsnorm(x, delta, self.weight, self.eps, dtype, rows)
 
     def stream_weight(self):
@@ -89,7 +101,9 @@ class NoNorm(Norm):
 
     def apply(self, x, delta, dtype, rows=None):
         if isinstance(delta, PostNormed):
-            return ops.postnorm_add_rmsnorm(x, delta.y, delta.weight, delta.eps, delta.mult, None, 0.0, dtype, rows, copy=True)
+            y, branches = _raw_branches(delta.y)
+            return ops.postnorm_add_rmsnorm(x, y, delta.weight, delta.eps, delta.mult, None, 0.0, dtype, rows, copy=True,
+                                            branches=branches)
         if delta is not None:
             if rows is not None:
                 raise ValueError("a plain delta is added to every row or to none")

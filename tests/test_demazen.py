@@ -440,7 +440,7 @@ def test_memory_kernels_continue_from_their_state_and_start_fresh_at_position_ze
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("hidden", [99, 320, 2048, 4100])
+@pytest.mark.parametrize("hidden", [99, 324, 2048, 4100])
 def test_two_raw_branches_ride_on_the_post_norm(hidden, dtype):
     """``x += rmsnorm(mean of the two branch norms) * w`` in one kernel against its restatement: every row, selected
     rows (the stream untouched), with a following norm and with the stream's rows handed on as they are."""

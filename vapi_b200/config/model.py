@@ -155,4 +155,4 @@ def _ensure_builtin() -> None:
 
 #: modules that ship with the package and register an architecture when imported
 BUILTIN_ARCHITECTURE_MODULES = ["vapi_b200.models.lfm2", "vapi_b200.models.vukavik", "vapi_b200.models.rapolix",
-                                "vapi_b200.models.demazen"]
+                                "vapi_b200.models.demazen", "vapi_b200.models.nelosun"]

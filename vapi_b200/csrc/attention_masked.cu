@@ -11,7 +11,9 @@
 // softmax's denominator also holds exp(sink_h) when sinks are given (no key, no value, unscaled);
 // head h's output is multiplied by sigmoid(gate[token, h]) when a gate is given.
 //
-// A cache page holds the keys [nkv, page_size, dk] and then the values [nkv, page_size, dv].
+// A cache page holds the keys [nkv, page_size, dk] and then the values [nkv, page_size, dv].  With `shared_kv` a
+// page holds the key rows alone and a key's value is the first dv elements of its own row (latent attention: the
+// cached latent is both, and the rotated key part follows it in the row); dv <= dk then.
 //
 // bfloat16 with keys and values of one width, 64 or 128, and pages of a multiple of 64 tokens runs on
 // the tensor cores: the flash kernel of attention_mma.cuh (four warps for prompt portions, one warp
@@ -60,7 +62,7 @@ masked_attention_kernel(const T* __restrict__ q, long long q_row_stride, const T
                         const T* __restrict__ gate, long long gate_stride, T* __restrict__ out,
                         float* __restrict__ part_o, float* __restrict__ part_ml, int nh, int nkv, int dk, int dv,
                         int page_size, int num_pages, float scale, int window, int chunk, int splits,
-                        int* __restrict__ status, int keep) {
+                        int* __restrict__ status, int keep, int shared_kv) {
     constexpr int DPL = DVMAX / 32;
     extern __shared__ __align__(16) float smem[];
     const int ldk = dk + 4, ldv = dv + 4;
@@ -68,6 +70,8 @@ masked_attention_kernel(const T* __restrict__ q, long long q_row_stride, const T
     float* Ks = Qs + MA_ROWS * ldk;        // [MA_BK][ldk]
     float* Vs = Ks + MA_BK * ldk;          // [MA_BK][ldv]
     float* Ps = Vs + MA_BK * ldv;          // [MA_WARPS][MA_RPW][MA_BK]
+    const float* Vr = shared_kv ? Ks : Vs;  // where a key tile's values are read
+    const int ldr = shared_kv ? ldk : ldv;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int s = blockIdx.z / splits, sp = blockIdx.z - s * splits;
@@ -95,7 +99,7 @@ masked_attention_kernel(const T* __restrict__ q, long long q_row_stride, const T
     const int per = (nt + splits - 1) / splits;
     const int it_begin = sp * per;
     const int it_end = min(nt, it_begin + per);
-    const size_t page_elems = (size_t)nkv * page_size * (dk + dv);
+    const size_t page_elems = (size_t)nkv * page_size * (shared_kv ? dk : dk + dv);
     const size_t v_base = (size_t)nkv * page_size * dk;
 
     for (int idx = threadIdx.x; idx < MA_ROWS * (dk / 4); idx += blockDim.x) {
@@ -142,7 +146,7 @@ masked_attention_kernel(const T* __restrict__ q, long long q_row_stride, const T
             }
             *reinterpret_cast<float4*>(Ks + jj * ldk + c4 * 4) = kv;
         }
-        for (int idx = threadIdx.x; idx < MA_BK * (dv / 4); idx += blockDim.x) {
+        for (int idx = threadIdx.x; idx < (shared_kv ? 0 : MA_BK * (dv / 4)); idx += blockDim.x) {
             const int jj = idx / (dv / 4), c4 = idx - jj * (dv / 4);
             const int j = kt * MA_BK + jj;
             float4 vv = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -196,7 +200,7 @@ masked_attention_kernel(const T* __restrict__ q, long long q_row_stride, const T
 #pragma unroll
             for (int c = 0; c < DPL; ++c) {
                 const int col = lane + 32 * c;
-                vcol[c] = col < dv ? Vs[jj * ldv + col] : 0.f;
+                vcol[c] = col < dv ? Vr[jj * ldr + col] : 0.f;
             }
 #pragma unroll
             for (int a = 0; a < MA_RPW; ++a) {
@@ -290,13 +294,15 @@ static int launch_masked(const void* q, long long q_row_stride, const void* cach
                          int table_stride, const int* cu_q, const int* seqlens_k, const float* sinks,
                          const void* gate, long long gate_stride, void* out, float* part_o, float* part_ml, int n,
                          int num_seqs, int max_q, int nh, int nkv, int dk, int dv, int page_size, int num_pages,
-                         float scale, int window, int chunk, int splits, int* status, cudaStream_t stream, int keep) {
+                         float scale, int window, int chunk, int splits, int* status, cudaStream_t stream, int keep,
+                         int shared_kv) {
     const int n_rep = nh / nkv;
     const int tiles = (max_q * n_rep + MA_ROWS - 1) / MA_ROWS;
     const size_t smem = sizeof(float) * ((size_t)(MA_ROWS + MA_BK) * (dk + 4) + (size_t)MA_BK * (dv + 4) +
                                          (size_t)MA_WARPS * MA_RPW * MA_BK);
     auto kern = masked_attention_kernel<T, DVMAX>;
     static size_t allowed = 0;
+    if (smem > 227 * 1024) return fail(-3, "masked_attention: heads of %d/%d need %zu bytes of shared memory", dk, dv, smem);
     if (smem > 48 * 1024 && smem > allowed) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return fail(-3, "masked_attention: %zu bytes of shared memory are not available", smem);
@@ -305,7 +311,7 @@ static int launch_masked(const void* q, long long q_row_stride, const void* cach
     dim3 grid(tiles, nkv, num_seqs * splits);
     cudaError_t e = launch(kern, grid, MA_WARPS * 32, smem, stream, (const T*)q, q_row_stride, (const T*)cache, block_table,
                            table_stride, cu_q, seqlens_k, sinks, (const T*)gate, gate_stride, (T*)out, part_o, part_ml, nh, nkv,
-                           dk, dv, page_size, num_pages, scale, window, chunk, splits, status, keep);
+                           dk, dv, page_size, num_pages, scale, window, chunk, splits, status, keep, shared_kv);
     int rc = check_launch("masked_attention", e);
     if (rc != 0 || splits == 1) return rc;
     const long long rows = (long long)n * nh;
@@ -320,18 +326,19 @@ VAPI_EXPORT int vapi_masked_attention(const void* q, long long q_row_stride, con
                                       long long gate_stride, void* out, float* part_o, float* part_ml, int n,
                                       int num_seqs, int max_q, int nh, int nkv, int dk, int dv, int page_size,
                                       int num_pages, float scale, int window, int chunk, int splits, int* status,
-                                      cudaStream_t stream, int keep) {
+                                      cudaStream_t stream, int keep, int shared_kv) {
     if (n <= 0 || num_seqs <= 0) return 0;
+    if (shared_kv && dv > dk) return fail(-1, "masked_attention: values of %d inside key rows of %d", dv, dk);
     if (keep < 0) return fail(-1, "masked_attention: %d kept first tokens", keep);
     if (window <= 0) keep = 0;
     if (nh <= 0 || nkv <= 0 || nh % nkv) return fail(-1, "masked_attention: %d heads over %d kv heads", nh, nkv);
-    if (dk <= 0 || dk % 4 || dv <= 0 || dv % 4 || dv > 256 || dk > 512)
-        return fail(-1, "masked_attention: head sizes %d/%d must be multiples of 4 (keys up to 512, values up to 256)", dk, dv);
+    if (dk <= 0 || dk % 4 || dv <= 0 || dv % 4 || dv > 512 || dk > 640)
+        return fail(-1, "masked_attention: head sizes %d/%d must be multiples of 4 (keys up to 640, values up to 512)", dk, dv);
     if (q_row_stride % 4) return fail(-1, "masked_attention: the query row stride %lld must be a multiple of 4", q_row_stride);
     if (splits < 1 || splits > 32) return fail(-1, "masked_attention: %d splits", splits);
     if (splits > 1 && (!part_o || !part_ml)) return fail(-1, "masked_attention: splits need scratch buffers");
     if (page_size <= 0 || num_pages <= 0) return fail(-1, "masked_attention: no pages");
-    if (dtype == VAPI_BF16 && dk == dv && (dk == 64 || dk == 128) && page_size % FA_BK == 0 && q_row_stride % 2 == 0 &&
+    if (!shared_kv && dtype == VAPI_BF16 && dk == dv && (dk == 64 || dk == 128) && page_size % FA_BK == 0 && q_row_stride % 2 == 0 &&
         nkv <= 65535 && (long long)num_seqs * splits <= 65535) {
         // the cache page is [2][nkv][page_size][d] when keys and values have one width: the layout of the fast kernels
         int rc;
@@ -363,15 +370,18 @@ VAPI_EXPORT int vapi_masked_attention(const void* q, long long q_row_stride, con
     }
 #define MA_GO(T, DV) return launch_masked<T, DV>(q, q_row_stride, cache, block_table, table_stride, cu_q, seqlens_k, sinks, gate, \
                                                  gate_stride, out, part_o, part_ml, n, num_seqs, max_q, nh, nkv, dk, dv,         \
-                                                 page_size, num_pages, scale, window, chunk, splits, status, stream, keep)
+                                                 page_size, num_pages, scale, window, chunk, splits, status, stream, keep,  \
+                                                 shared_kv)
     if (dtype == VAPI_F32) {
         if (dv <= 64) MA_GO(float, 64);
         if (dv <= 128) MA_GO(float, 128);
-        MA_GO(float, 256);
+        if (dv <= 256) MA_GO(float, 256);
+        MA_GO(float, 512);
     } else if (dtype == VAPI_BF16) {
         if (dv <= 64) MA_GO(__nv_bfloat16, 64);
         if (dv <= 128) MA_GO(__nv_bfloat16, 128);
-        MA_GO(__nv_bfloat16, 256);
+        if (dv <= 256) MA_GO(__nv_bfloat16, 256);
+        MA_GO(__nv_bfloat16, 512);
     }
 #undef MA_GO
     return fail(-2, "masked_attention: unsupported dtype %d", dtype);

@@ -10,14 +10,14 @@
 using namespace vapi;
 
 // ---------------------------------------------------------------------------
-// embedding: out[r, :] = float(table[tokens[r], :])
+// embedding: out[r, :] = float(table[tokens[r], :]) * scale
 // For a norm that follows (optional): ss = the sum of squares of each produced row, [1][n];
 // xw = bfloat16(row * next_w), [n][hidden].
 template <typename TW>
 __global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict__ tokens,
                              float* __restrict__ out, float* __restrict__ ss,
                              const float* __restrict__ next_w, __nv_bfloat16* __restrict__ xw,
-                             int n, int hidden, int vocab, int* __restrict__ status) {
+                             int n, int hidden, int vocab, int* __restrict__ status, float scale) {
     __shared__ float red[33];
     const int r = blockIdx.x;
     pdl_trigger();
@@ -32,7 +32,7 @@ __global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict
     float* dst = out + (size_t)r * hidden;
     float acc = 0.f;
     for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
-        const float v = to_f32(src[c]);
+        const float v = to_f32(src[c]) * scale;
         dst[c] = v;
         if (xw) xw[(size_t)r * hidden + c] = __float2bfloat16_rn(v * next_w[c]);
         acc += v * v;
@@ -45,16 +45,16 @@ __global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict
 
 VAPI_EXPORT int vapi_embed(const void* table, int table_dtype, const int* tokens, float* out,
                            float* ss, const float* next_w, void* xw, int n, int hidden, int vocab,
-                           int* status, cudaStream_t stream) {
+                           int* status, cudaStream_t stream, float scale) {
     if (xw && !next_w) return fail(-1, "embed: a weighted copy needs the next norm's weight");
     if (n <= 0) return 0;
     if (hidden <= 0 || vocab <= 0) return fail(-1, "embed: bad sizes hidden=%d vocab=%d", hidden, vocab);
     const int threads = hidden >= 1024 ? 256 : 128;
     cudaError_t e;
     if (table_dtype == VAPI_F32)
-        e = launch(embed_kernel<float>, n, threads, 0, stream, (const float*)table, tokens, out, ss, next_w, (__nv_bfloat16*)xw, n, hidden, vocab, status);
+        e = launch(embed_kernel<float>, n, threads, 0, stream, (const float*)table, tokens, out, ss, next_w, (__nv_bfloat16*)xw, n, hidden, vocab, status, scale);
     else if (table_dtype == VAPI_BF16)
-        e = launch(embed_kernel<__nv_bfloat16>, n, threads, 0, stream, (const __nv_bfloat16*)table, tokens, out, ss, next_w, (__nv_bfloat16*)xw, n, hidden, vocab, status);
+        e = launch(embed_kernel<__nv_bfloat16>, n, threads, 0, stream, (const __nv_bfloat16*)table, tokens, out, ss, next_w, (__nv_bfloat16*)xw, n, hidden, vocab, status, scale);
     else
         return fail(-2, "embed: unsupported table dtype %d", table_dtype);
     return check_launch("embed", e);
@@ -222,6 +222,140 @@ VAPI_EXPORT int vapi_add_rmsnorm(float* x, const void* delta, const float* w, fl
     else
         return fail(-2, "add_rmsnorm: unsupported dtype %d", out_dtype);
     return check_launch("add_rmsnorm", e);
+}
+
+// Two sublayers side by side, each with a scale per column (layer scale), folded into the stream by the kernel
+// that reads it next:  x += s1 * y1 + s2 * y2  (y2 may be absent; a scale may be absent and then counts as one),
+// then out = rmsnorm(x) * w, or, without w, the rows of x themselves in T (for a reader that takes the stream as
+// it is).  `out` has rows of `out_stride` elements, so that it may be the left part of a wider buffer.  rows as
+// for add_rmsnorm.  Everything is float but the two loads and the store.
+template <typename T>
+__global__ void scaled_add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ y1, const float* __restrict__ s1,
+                                          const T* __restrict__ y2, const float* __restrict__ s2,
+                                          const float* __restrict__ w, float eps, const int* __restrict__ rows,
+                                          T* __restrict__ out, long long out_stride, int n_out, int hidden, int write_x) {
+    __shared__ float red[33];
+    const int j = blockIdx.x;
+    pdl_trigger();
+    pdl_wait();
+    if (j >= n_out) return;
+    const int row = rows ? rows[j] : j;
+    float* xr = x + (size_t)row * hidden;
+    const T* a = y1 ? y1 + (size_t)row * hidden : nullptr;
+    const T* b = y2 ? y2 + (size_t)row * hidden : nullptr;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+        float v = xr[c];
+        if (a) v += (s1 ? s1[c] : 1.f) * to_f32(a[c]);
+        if (b) v += (s2 ? s2[c] : 1.f) * to_f32(b[c]);
+        if ((a || b) && write_x) xr[c] = v;
+        ss += v * v;
+    }
+    if (!out) return;
+    float inv = 1.f;
+    if (w) {
+        ss = block_sum(ss, red);
+        inv = rsqrtf(ss / (float)hidden + eps);
+    }
+    T* orow = out + (size_t)j * out_stride;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+        float v = xr[c];
+        if (!write_x) {
+            if (a) v += (s1 ? s1[c] : 1.f) * to_f32(a[c]);
+            if (b) v += (s2 ? s2[c] : 1.f) * to_f32(b[c]);
+        }
+        orow[c] = from_f32<T>(w ? v * inv * w[c] : v);
+    }
+}
+
+// The same with 16-byte accesses and the row held in registers (hidden a multiple of 4, at most 4 * NORM_KMAX *
+// blockDim elements, out_stride a multiple of 4 and every pointer 16-byte aligned).
+template <typename T>
+__global__ void scaled_add_rmsnorm_vec_kernel(float* __restrict__ x, const T* __restrict__ y1, const float* __restrict__ s1,
+                                              const T* __restrict__ y2, const float* __restrict__ s2,
+                                              const float* __restrict__ w, float eps, const int* __restrict__ rows,
+                                              T* __restrict__ out, long long out_stride, int n_out, int hidden,
+                                              int write_x) {
+    __shared__ float red[33];
+    const int j = blockIdx.x;
+    pdl_trigger();
+    pdl_wait();
+    if (j >= n_out) return;
+    const int row = rows ? rows[j] : j;
+    float* xr = x + (size_t)row * hidden;
+    const T* a = y1 ? y1 + (size_t)row * hidden : nullptr;
+    const T* b = y2 ? y2 + (size_t)row * hidden : nullptr;
+    const int h4 = hidden >> 2;
+    float4 v[NORM_KMAX];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < NORM_KMAX; ++k) {
+        const int c = threadIdx.x + k * blockDim.x;
+        v[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (c < h4) {
+            v[k] = Pack4<float>::load(xr + 4 * c);
+            if (a) {
+                const float4 d = Pack4<T>::load(a + 4 * c);
+                const float4 s = s1 ? Pack4<float>::load(s1 + 4 * c) : make_float4(1.f, 1.f, 1.f, 1.f);
+                v[k].x += s.x * d.x; v[k].y += s.y * d.y; v[k].z += s.z * d.z; v[k].w += s.w * d.w;
+            }
+            if (b) {
+                const float4 d = Pack4<T>::load(b + 4 * c);
+                const float4 s = s2 ? Pack4<float>::load(s2 + 4 * c) : make_float4(1.f, 1.f, 1.f, 1.f);
+                v[k].x += s.x * d.x; v[k].y += s.y * d.y; v[k].z += s.z * d.z; v[k].w += s.w * d.w;
+            }
+            if ((a || b) && write_x) Pack4<float>::store(xr + 4 * c, v[k]);
+            ss += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+        }
+    }
+    if (!out) return;
+    float inv = 1.f;
+    if (w) {
+        ss = block_sum(ss, red);
+        inv = rsqrtf(ss / (float)hidden + eps);
+    }
+    T* orow = out + (size_t)j * out_stride;
+#pragma unroll
+    for (int k = 0; k < NORM_KMAX; ++k) {
+        const int c = threadIdx.x + k * blockDim.x;
+        if (c < h4) {
+            float4 o = v[k];
+            if (w) {
+                const float4 wv = Pack4<float>::load(w + 4 * c);
+                o = make_float4(o.x * inv * wv.x, o.y * inv * wv.y, o.z * inv * wv.z, o.w * inv * wv.w);
+            }
+            Pack4<T>::store(orow + 4 * c, o);
+        }
+    }
+}
+
+VAPI_EXPORT int vapi_scaled_add_rmsnorm(float* x, const void* y1, const float* s1, const void* y2, const float* s2,
+                                        const float* w, float eps, const int* rows, void* out, long long out_stride,
+                                        int dtype, int n_out, int hidden, cudaStream_t stream) {
+    if (n_out <= 0) return 0;
+    if (hidden <= 0) return fail(-1, "scaled_add_rmsnorm: hidden=%d", hidden);
+    if (!y1 && y2) return fail(-1, "scaled_add_rmsnorm: the second sublayer comes with a first");
+    if (out && out_stride < hidden) return fail(-1, "scaled_add_rmsnorm: output rows of %lld elements for a width of %d", out_stride, hidden);
+    if (!out && rows) return fail(-1, "scaled_add_rmsnorm: selected rows leave the stream alone, so an output is needed");
+    const int write_x = rows ? 0 : 1;
+    const int esz = dtype == VAPI_F32 ? 4 : 2;
+    const bool aligned = ((uintptr_t)x & 15) == 0 && (((uintptr_t)y1 | (uintptr_t)y2) & (4 * esz - 1)) == 0 &&
+                         (((uintptr_t)s1 | (uintptr_t)s2 | (uintptr_t)w) & 15) == 0 &&
+                         ((uintptr_t)out & (4 * esz - 1)) == 0 && out_stride % 4 == 0;
+    const int vt = hidden >= 1024 ? 256 : 128;
+    const bool vec = hidden % 4 == 0 && hidden / 4 <= NORM_KMAX * vt && aligned;
+    const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+    cudaError_t e;
+#define SAR_GO(T)                                                                                                          \
+    e = vec ? launch(scaled_add_rmsnorm_vec_kernel<T>, n_out, vt, 0, stream, x, (const T*)y1, s1, (const T*)y2, s2, w, eps,   \
+                     rows, (T*)out, out_stride, n_out, hidden, write_x)                                                       \
+            : launch(scaled_add_rmsnorm_kernel<T>, n_out, threads, 0, stream, x, (const T*)y1, s1, (const T*)y2, s2, w, eps,  \
+                     rows, (T*)out, out_stride, n_out, hidden, write_x)
+    if (dtype == VAPI_F32) SAR_GO(float);
+    else if (dtype == VAPI_BF16) SAR_GO(__nv_bfloat16);
+    else return fail(-2, "scaled_add_rmsnorm: unsupported dtype %d", dtype);
+#undef SAR_GO
+    return check_launch("scaled_add_rmsnorm", e);
 }
 
 // residual add alone (used at the very end of a step when nothing follows the

@@ -18,6 +18,10 @@
 // hid[pos] = silu(W_gate[e] h) * (W_up[e] h) from one matrix whose rows alternate gate, up; down: y[pair] = weight *
 // W_down[e] hid[pos] in float; the sum over a token's pairs, its identity experts and the shared expert
 // is taken in a fixed order.
+// The gated form has three constants: out = g' * sigmoid(alpha * g') * (u' + shift) with g' = min(g, limit) and
+// u' = clamp(u, -limit, limit) when limit > 0, else g' = g, u' = u.  alpha = 1, shift = 0 and no limit is SiLU gating.
+// A third way of choosing needs no router at all (moe_table_route): a table [vocab, top] of expert indices, read at
+// the token's id, names the token's experts, each with weight 1 / top.
 #include "common.cuh"
 #include "mma_tile.cuh"
 
@@ -228,6 +232,39 @@ __global__ void moe_plan_kernel(const int* __restrict__ ids, int* __restrict__ r
     }
 }
 
+// what a gated expert makes of a gate row's and an up row's product (see the top of the file)
+__device__ __forceinline__ float gated_act(float g, float u, float limit, float alpha, float shift) {
+    if (limit > 0.f) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+    }
+    return g / (1.f + expf(-alpha * g)) * (u + shift);
+}
+
+// ids[t, k] = table[token[t], k], each with weight 1 / top.  A token id outside the table is a status, not a read.
+__global__ void moe_table_route_kernel(const int* __restrict__ tokens, const int* __restrict__ table, int vocab,
+                                       int* __restrict__ ids, float* __restrict__ wts, int n, int top, int experts,
+                                       int* __restrict__ status) {
+    const int p = blockIdx.x * blockDim.x + threadIdx.x;
+    pdl_trigger();
+    pdl_wait();
+    if (p >= n * top) return;
+    const int t = p / top, k = p - t * top;
+    const int tok = tokens[t];
+    int e = 0;
+    if (tok < 0 || tok >= vocab) {
+        if (status) atomicExch(status, 1);
+    } else {
+        e = table[(size_t)tok * top + k];
+        if (e < 0 || e >= experts) {
+            if (status) atomicExch(status, 1);
+            e = 0;
+        }
+    }
+    ids[p] = e;
+    wts[p] = 1.f / (float)top;
+}
+
 // out rows of one tile = act(A rows x W[e]^T): A [*, K] rows gathered through `src` (pair / src_div when
 // gather, else the sorted position itself), W [experts, N, K].  MODE 0 (up): out[pos, :] = relu(.)^2 in T.
 // MODE 1 (down): out[pair, :] = weight[pair] * (.) in float.  MODE 2 (gate and up in one matrix, rows alternating
@@ -237,7 +274,7 @@ __global__ void __launch_bounds__(256)
 moe_grouped_kernel(const T* __restrict__ A, long long a_stride, const T* __restrict__ W, const int* __restrict__ plan,
                    const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
                    const int* __restrict__ offsets, const int* __restrict__ pair_of, const float* __restrict__ wts,
-                   void* __restrict__ out, int N, int K, int top) {
+                   void* __restrict__ out, int N, int K, int top, float act_limit, float act_alpha, float act_shift) {
     __shared__ float As[MOE_TK][MOE_TM + 4];
     __shared__ float Ws[MOE_TK][MOE_TN + 4];
     __shared__ int s_src[MOE_TM], s_dst[MOE_TM];
@@ -302,8 +339,8 @@ moe_grouped_kernel(const T* __restrict__ A, long long a_stride, const T* __restr
             for (int j = 0; j < 4; j += 2) {
                 const int c = c0 + tx * 4 + j;
                 if (c + 1 >= N) continue;
-                const float gv = acc[i][j], uv = acc[i][j + 1];
-                reinterpret_cast<T*>(out)[(size_t)dst * (N >> 1) + (c >> 1)] = from_f32<T>(gv / (1.f + expf(-gv)) * uv);
+                reinterpret_cast<T*>(out)[(size_t)dst * (N >> 1) + (c >> 1)] =
+                    from_f32<T>(gated_act(acc[i][j], acc[i][j + 1], act_limit, act_alpha, act_shift));
             }
         } else {
 #pragma unroll
@@ -327,7 +364,7 @@ __global__ void __launch_bounds__(WM * WN * 32)
 moe_grouped_mma_kernel(const __nv_bfloat16* __restrict__ A, long long a_stride, const __nv_bfloat16* __restrict__ W,
                        const int* __restrict__ plan, const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
                        const int* __restrict__ offsets, const int* __restrict__ pair_of, const float* __restrict__ wts,
-                       void* __restrict__ out, int N, int K, int top) {
+                       void* __restrict__ out, int N, int K, int top, float act_limit, float act_alpha, float act_shift) {
     extern __shared__ __align__(128) unsigned char moe_smem[];
     using Tile = MmaTile<BM, BN, WM, WN>;
     __shared__ const __nv_bfloat16* a_rows[BM];
@@ -374,7 +411,7 @@ moe_grouped_mma_kernel(const __nv_bfloat16* __restrict__ A, long long a_stride, 
                     // (c is even: v0 is a gate's row, v1 the up row that belongs to it)
                     if (c + 1 < N)
                         reinterpret_cast<__nv_bfloat16*>(out)[(size_t)dst * (N >> 1) + (c >> 1)] =
-                            __float2bfloat16_rn(v0 / (1.f + expf(-v0)) * v1);
+                            __float2bfloat16_rn(gated_act(v0, v1, act_limit, act_alpha, act_shift));
                 } else if (MODE == 0) {
                     const float r0 = fmaxf(v0, 0.f), r1 = fmaxf(v1, 0.f);
                     __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)dst * N + c;
@@ -491,12 +528,31 @@ VAPI_EXPORT int vapi_moe_route(const void* h, int dtype, const float* wr, const 
     return check_launch("moe_plan", e);
 }
 
+// The router-less choice: ids and weights from a table over the token ids, then the same plan.
+VAPI_EXPORT int vapi_moe_table_route(const int* tokens, const int* table, int vocab, int* ids, float* wts, int* ranks,
+                                     int* offsets, int* pair_of, int* plan, int* tile_expert, int* tile_row0, int n,
+                                     int experts, int top, int* status, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (experts <= 0 || top <= 0 || top > experts || vocab <= 0)
+        return fail(-1, "moe_table_route: %d experts, top %d, a table of %d rows", experts, top, vocab);
+    const int pairs = n * top;
+    cudaError_t e = launch(moe_table_route_kernel, (pairs + 255) / 256, 256, 0, stream, tokens, table, vocab, ids, wts, n, top,
+                           experts, status);
+    int rc = check_launch("moe_table_route", e);
+    if (rc != 0) return rc;
+    const size_t psm = sizeof(int) * (size_t)(2 * experts + 1);
+    if (psm > 48 * 1024) return fail(-1, "moe_table_route: %d experts are too many", experts);
+    e = launch(moe_plan_kernel, 1, 1024, psm, stream, (const int*)ids, ranks, offsets, pair_of, plan, tile_expert, tile_row0,
+               pairs, experts, moe_tile_rows(pairs, experts));
+    return check_launch("moe_plan", e);
+}
+
 // mode 0: out = hid [n * top, N] in the activation type from A = h [n, K]; mode 1: out = y [n * top, N] float
 // from A = hid [n * top, K].
 VAPI_EXPORT int vapi_moe_grouped(const void* A, long long a_stride, const void* W, int dtype, const int* plan,
                                  const int* tile_expert, const int* tile_row0, const int* offsets, const int* pair_of,
                                  const float* wts, void* out, int pairs, int experts, int N, int K, int top, int mode,
-                                 cudaStream_t stream) {
+                                 cudaStream_t stream, float act_limit, float act_alpha, float act_shift) {
     if (pairs <= 0 || experts <= 0) return 0;
     if (mode < 0 || mode > 2 || (mode == 2 && (N & 1))) return fail(-1, "moe_grouped: mode %d with %d output rows", mode, N);
     const int max_tiles = pairs / MOE_TM + experts;
@@ -517,7 +573,7 @@ VAPI_EXPORT int vapi_moe_grouped(const void* A, long long a_stride, const void* 
         }                                                                                                                    \
         dim3 g(pairs / BM_ + experts, (N + BN_ - 1) / BN_);                                                                  \
         e = launch(kern, g, Tile::THREADS, Tile::SMEM, stream, (const __nv_bfloat16*)A, a_stride, (const __nv_bfloat16*)W,   \
-                   plan, tile_expert, tile_row0, offsets, pair_of, wts, out, N, K, top);                                     \
+                   plan, tile_expert, tile_row0, offsets, pair_of, wts, out, N, K, top, act_limit, act_alpha, act_shift);    \
     } while (0)
         if (mode == 0) MOE_TC(0, 64, 64, 2, 2); else if (mode == 1) MOE_TC(1, 64, 64, 2, 2); else MOE_TC(2, 64, 64, 2, 2);
 #undef MOE_TC
@@ -526,7 +582,7 @@ VAPI_EXPORT int vapi_moe_grouped(const void* A, long long a_stride, const void* 
     if (tile_m != MOE_TM) return fail(-1, "moe_grouped: the float kernel has tiles of %d rows", MOE_TM);
 #define MOE_GO(T, M)                                                                                                         \
     e = launch(moe_grouped_kernel<T, M>, grid, 256, 0, stream, (const T*)A, a_stride, (const T*)W, plan, tile_expert,         \
-               tile_row0, offsets, pair_of, wts, out, N, K, top)
+               tile_row0, offsets, pair_of, wts, out, N, K, top, act_limit, act_alpha, act_shift)
     if (dtype == VAPI_F32) { if (mode == 0) MOE_GO(float, 0); else if (mode == 1) MOE_GO(float, 1); else MOE_GO(float, 2); }
     else if (dtype == VAPI_BF16) {
         if (mode == 0) MOE_GO(__nv_bfloat16, 0); else if (mode == 1) MOE_GO(__nv_bfloat16, 1); else MOE_GO(__nv_bfloat16, 2);

@@ -323,7 +323,8 @@ __global__ void qk_norm_rope_write_split_kernel(T* __restrict__ qkv, long long r
                                                 int rot, int interleaved, T* __restrict__ cache,
                                                 const int* __restrict__ slot_mapping, int n, int nh, int nkv,
                                                 int dk, int dv, int page_size, int num_pages,
-                                                int* __restrict__ status) {
+                                                int* __restrict__ status, const int* __restrict__ positions,
+                                                float qt_coef, int qt_every) {
     __shared__ float sh[QK_WARPS][QK_MAX_D];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int heads = nh + 2 * nkv;
@@ -341,6 +342,8 @@ __global__ void qk_norm_rope_write_split_kernel(T* __restrict__ qkv, long long r
     T* src = qkv + (size_t)t * row_stride + (is_q || is_k ? (size_t)h * dk : (size_t)(nh + nkv) * dk + (size_t)(h - nh - nkv) * dv);
     const float* w = is_q ? qw : (is_k ? kw : nullptr);
     const bool rope = (is_q || is_k) && cosr != nullptr;
+    // a query temperature: q at position p is multiplied by 1 + coef * ln(floor((p + 1) / every) + 1)
+    const float q_mult = (is_q && qt_every > 0) ? 1.f + qt_coef * logf((float)((positions[t] + 1) / qt_every + 1)) : 1.f;
     float* s = sh[warp];
     float ss = 0.f;
     for (int i = lane; i < d; i += 32) {
@@ -356,6 +359,7 @@ __global__ void qk_norm_rope_write_split_kernel(T* __restrict__ qkv, long long r
     __syncwarp();
     T* dst = nullptr;
     if (is_q) {
+        if (!w && !rope && q_mult == 1.f) return;      // nothing changes a query that is neither normed, rotated nor scaled
         dst = src;
     } else if (cache) {
         const int page = slot / page_size, off = slot - page * page_size;
@@ -383,7 +387,7 @@ __global__ void qk_norm_rope_write_split_kernel(T* __restrict__ qkv, long long r
             const float c = cosr[(size_t)t * half + j], sn = sinr[(size_t)t * half + j];
             v = first ? v * c - pv * sn : v * c + pv * sn;
         }
-        dst[i] = from_f32<T>(v);
+        dst[i] = from_f32<T>(v * q_mult);
     }
 }
 
@@ -479,8 +483,10 @@ VAPI_EXPORT int vapi_qk_norm_rope_write_split(void* qkv, long long row_stride, i
                                               float eps, const float* cosr, const float* sinr, int rot, int interleaved,
                                               void* cache, const int* slot_mapping, int n, int nh, int nkv, int dk,
                                               int dv, int page_size, int num_pages, int whole, int* status,
-                                              cudaStream_t stream) {
+                                              cudaStream_t stream, const int* positions, float qt_coef, int qt_every) {
     if (n <= 0) return 0;
+    if (qt_every < 0 || (qt_every > 0 && (!positions || whole)))
+        return fail(-1, "qk_norm_rope_write_split: a query temperature needs the positions and norms per head");
     if (dk <= 0 || dk > QK_MAX_D || dv <= 0 || dv > QK_MAX_D)
         return fail(-1, "qk_norm_rope_write_split: head sizes %d/%d are outside 1..%d", dk, dv, QK_MAX_D);
     if (cosr && (rot <= 0 || rot > dk || (rot % 2) != 0))
@@ -508,11 +514,12 @@ VAPI_EXPORT int vapi_qk_norm_rope_write_split(void* qkv, long long row_stride, i
     }
     if (dtype == VAPI_F32)
         e = launch(qk_norm_rope_write_split_kernel<float>, blocks, QK_WARPS * 32, 0, stream, (float*)qkv, row_stride, qw, kw, eps,
-                   cosr, sinr, rot, interleaved, (float*)cache, slot_mapping, n, nh, nkv, dk, dv, page_size, num_pages, status);
+                   cosr, sinr, rot, interleaved, (float*)cache, slot_mapping, n, nh, nkv, dk, dv, page_size, num_pages, status,
+                   positions, qt_coef, qt_every);
     else if (dtype == VAPI_BF16)
         e = launch(qk_norm_rope_write_split_kernel<__nv_bfloat16>, blocks, QK_WARPS * 32, 0, stream, (__nv_bfloat16*)qkv,
                    row_stride, qw, kw, eps, cosr, sinr, rot, interleaved, (__nv_bfloat16*)cache, slot_mapping, n, nh, nkv,
-                   dk, dv, page_size, num_pages, status);
+                   dk, dv, page_size, num_pages, status, positions, qt_coef, qt_every);
     else
         return fail(-2, "qk_norm_rope_write_split: unsupported dtype %d", dtype);
     return check_launch("qk_norm_rope_write_split", e);

@@ -94,7 +94,8 @@ class ModelRunner:
         self._site_buffers = {s: self.cache.site_buffers(s) for s in set(flat)}
         #: whether every block has the stream form that steps of few rows run (blocks without it hand
         #: their output on in another shape than a plain delta, so such a model takes the ordinary path)
-        self._stream_form = all(hasattr(b, "forward_stream") for b in plan.layers)
+        self._stream_form = all(hasattr(b, "forward_stream") for b in plan.layers) and not plan.stream_parts
+        self._keep_embedding = any(getattr(p, "needs_embedding_output", False) for p in plan.stream_parts.values())
         self.steps_run = 0
         self.graph_max_batch = min(64, max_requests)
         self._graphs: Dict[int, Any] = {}
@@ -191,8 +192,15 @@ class ModelRunner:
         if ctx.fused:
             return self._forward_few_rows(ctx, views)
         x = plan.embedding.forward(ctx)
+        if plan.stream_parts:
+            ctx.extras.clear()          # what a stream part kept belongs to one run of the step (a captured step runs thrice)
+        if self._keep_embedding:
+            # (a stream part in front of the first layer replaces the stream without writing it: no copy then)
+            ctx.extras["embedding_output"] = x if plan.order and plan.order[0].before is not None else x.clone()
         delta = None
         for i, call in enumerate(plan.order):
+            if call.before is not None:
+                x, delta = plan.stream_parts[call.before].forward(x, delta, ctx)
             delta = plan.layers[call.layer].forward(x, delta, ctx, views[i])
         if ctx.logits_rows is None:
             return None

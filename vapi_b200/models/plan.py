@@ -17,11 +17,13 @@ class LayerCall:
     ``layer`` indexes ``ModelPlan.layers`` (a layer may be named more than once: its weights
     are shared, each call site has a cache of its own).  ``cache_of`` = k makes this call
     site read the cache that call site k owns instead of having one (k < this index, and
-    that site's mixer must want the same kind of cache).
+    that site's mixer must want the same kind of cache).  ``before`` names an entry of ``ModelPlan.stream_parts``
+    that acts on the residual stream right before this call (a looped stack's input product).
     """
 
     layer: int
     cache_of: Optional[int] = None
+    before: Optional[str] = None
 
 
 @dataclass
@@ -40,6 +42,9 @@ class ModelPlan:
     position_encodings: List[PositionEncoding] = field(default_factory=list)
     eos_token_ids: Tuple[int, ...] = ()
     config: Any = None
+    #: parts that act on the whole stream between layers (``part.forward(x, pending, ctx) -> (x, pending)``), by the
+    #: key that ``LayerCall.before`` names; their tensors carry no layer prefix
+    stream_parts: Dict[str, Part] = field(default_factory=dict)
 
     def __post_init__(self) -> None:
         if len(self.layers) != len(self.layer_prefixes):
@@ -47,6 +52,8 @@ class ModelPlan:
         for i, c in enumerate(self.order):
             if not 0 <= c.layer < len(self.layers):
                 raise ValueError(f"run order entry {i} names layer {c.layer} of {len(self.layers)}")
+            if c.before is not None and c.before not in self.stream_parts:
+                raise ValueError(f"run order entry {i} names the stream part `{c.before}`, which the plan does not have")
             if c.cache_of is not None:
                 if not 0 <= c.cache_of < i or self.order[c.cache_of].cache_of is not None:
                     raise ValueError(f"run order entry {i}: cache_of must name an earlier entry that owns its cache")
@@ -64,6 +71,8 @@ class ModelPlan:
         specs += self.head.tensor_specs("")
         for pe in self.position_encodings:
             specs += pe.tensor_specs("")
+        for part in self.stream_parts.values():
+            specs += part.tensor_specs("")
         seen: Dict[str, TensorSpec] = {}
         for s in specs:
             if s.name in seen and seen[s.name].shape != s.shape:
@@ -79,6 +88,8 @@ class ModelPlan:
         self.head.bind(tensors, "", dtype)
         for pe in self.position_encodings:
             pe.bind(tensors, "", dtype)
+        for part in self.stream_parts.values():
+            part.bind(tensors, "", dtype)
 
     # ---- caches --------------------------------------------------------------------
     def cache_sites(self) -> List[Tuple[object, object]]:

@@ -176,8 +176,9 @@ def sm_count() -> int:
 
 # ---------------------------------------------------------------------------------------
 def embed(table: torch.Tensor, tokens: torch.Tensor, status: Optional[torch.Tensor] = None,
-          next_weight: Optional[torch.Tensor] = None):
-    """Rows of ``table`` [V, H] for ``tokens`` [n] as the float32 residual stream [n, H].
+          next_weight: Optional[torch.Tensor] = None, scale: float = 1.0):
+    """Rows of ``table`` [V, H] for ``tokens`` [n], times ``scale`` (a float32 product), as the float32 residual
+    stream [n, H].
 
     With ``next_weight`` (the weight of the norm that will read the stream) the call also
     returns what a deferred norm needs: the sums of squares of the rows, [1, n], and
@@ -194,7 +195,7 @@ def embed(table: torch.Tensor, tokens: torch.Tensor, status: Optional[torch.Tens
         xw = torch.empty((n, hidden), dtype=torch.bfloat16, device=table.device)
     lib = _lib("elementwise")
     _check(lib, lib.vapi_embed(_p(table), _dt(table), _p(tokens), _p(out), _p(ss), _p(next_weight), _p(xw), n,
-                               hidden, vocab, _p(status), _stream()))
+                               hidden, vocab, _p(status), _stream(), ctypes.c_float(scale)))
     return (out, ss, xw) if next_weight is not None else out
 
 
@@ -1065,6 +1066,106 @@ def postnorm_add_rmsnorm(x: torch.Tensor, y: Optional[torch.Tensor], post_weight
     return out
 
 
+def scaled_add_rmsnorm(x: torch.Tensor, y1: Optional[torch.Tensor], s1: Optional[torch.Tensor], y2: Optional[torch.Tensor],
+                       s2: Optional[torch.Tensor], weight: Optional[torch.Tensor], eps: float, out_dtype: torch.dtype,
+                       rows: Optional[torch.Tensor] = None, copy: bool = False,
+                       out: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """``x += s1 * y1 + s2 * y2`` on the float32 stream (two sublayers side by side, each with a scale per column; a
+    missing scale counts as one, ``y2`` or both may be missing) and, with ``weight``, ``out = rmsnorm(x) * weight`` in
+    the same pass.  ``weight`` None with ``copy``: the rows of the stream themselves in ``out_dtype``; without
+    ``copy`` only the stream is updated (returns None).  With ``rows`` only those rows are produced and ``x`` is left
+    untouched.  ``out`` may be given: [rows, >= hidden] with unit inner stride, e.g. the left part of a wider buffer."""
+    _cuda(x, y1, s1, y2, s2, weight, rows, out)
+    _f32(x, "residual stream")
+    _f32(s1, "layer scale")
+    _f32(s2, "layer scale")
+    _f32(weight, "norm weight")
+    _i32(rows, "rows")
+    hidden = x.shape[-1]
+    for y in (y1, y2):
+        if y is not None:
+            _contig(y, "sublayer output")
+            if y.shape != x.shape or y.dtype != out_dtype:
+                raise KernelError("a sublayer's output must have the stream's shape and the activation dtype")
+    for v in (s1, s2, weight):
+        if v is not None and v.numel() != hidden:
+            raise KernelError(f"scales and norm weights must have {hidden} elements")
+    n_out = rows.numel() if rows is not None else x.shape[0]
+    wants = weight is not None or copy
+    if y1 is None and y2 is None and not wants:
+        return None
+    if y1 is None and y2 is not None:
+        y1, s1, y2, s2 = y2, s2, None, None
+    if wants:
+        if out is None:
+            out = torch.empty((n_out, hidden), dtype=out_dtype, device=x.device)
+        elif out.dtype != out_dtype or out.dim() != 2 or out.shape[0] != n_out or out.shape[1] != hidden or out.stride(1) != 1:
+            raise KernelError("the given output must be [rows, hidden] of the activation dtype with unit inner stride")
+    else:
+        out = None
+    lib = _lib("elementwise")
+    _check(lib, lib.vapi_scaled_add_rmsnorm(_p(x), _p(y1), _p(s1), _p(y2), _p(s2), _p(weight), ctypes.c_float(eps), _p(rows),
+                                            _p(out), ctypes.c_longlong(out.stride(0) if out is not None else 0),
+                                            _DT[out_dtype], n_out, hidden, _stream()))
+    return out
+
+
+def latent_prepare(down: torch.Tensor, q_rank: int, kv_rank: int, rot_dim: int, q_weight: Optional[torch.Tensor],
+                   kv_weight: torch.Tensor, eps: float, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], rot: int,
+                   cache_layer: Optional[torch.Tensor], page_size: int, slot_mapping: Optional[torch.Tensor],
+                   out_dtype: torch.dtype, status: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """Latent attention's cache write.  ``down`` [n, >= q_rank + kv_rank + rot_dim] float32 holds a token's three
+    down-projections.  Returns the query latent ``rmsnorm(down[:, :q_rank]) * q_weight`` [n, q_rank] in ``out_dtype``
+    (None for ``q_rank`` 0) and writes ``rmsnorm(latent) * kv_weight | rotate(key part)`` as the token's row of
+    ``cache_layer``, flat pages [pages, page_size * (kv_rank + rot_dim)].  The rotation pairs element i with
+    i + rot/2 over the first ``rot`` elements of the key part; ``cos``/``sin`` [n, rot/2] float32."""
+    _cuda(down, q_weight, kv_weight, cos, sin, cache_layer, slot_mapping)
+    _f32(q_weight, "query latent norm weight")
+    _f32(kv_weight, "latent norm weight")
+    _f32(cos, "cos")
+    _f32(sin, "sin")
+    _i32(slot_mapping, "slot mapping")
+    if down.dtype != torch.float32 or down.dim() != 2 or down.stride(1) != 1:
+        raise KernelError("the down-projections must be float32 [n, columns] with unit inner stride")
+    n = down.shape[0]
+    if (q_rank > 0 and (q_weight is None or q_weight.numel() != q_rank)) or kv_weight.numel() != kv_rank:
+        raise KernelError("norm weights must be as wide as their latents")
+    if rot > 0 and (cos is None or sin is None or cos.shape != (n, rot // 2) or sin.shape != cos.shape):
+        raise KernelError("cos/sin must be [n, rot/2]")
+    num_pages = 0
+    if cache_layer is not None:
+        _contig(cache_layer, "cache layer")
+        if cache_layer.dtype != out_dtype or cache_layer.dim() != 2 or cache_layer.shape[1] != page_size * (kv_rank + rot_dim):
+            raise KernelError(f"cache layer {tuple(cache_layer.shape)} / {cache_layer.dtype} does not fit pages of "
+                              f"{page_size} x ({kv_rank} + {rot_dim}) {out_dtype}")
+        num_pages = cache_layer.shape[0]
+    cq = torch.empty((n, q_rank), dtype=out_dtype, device=down.device) if q_rank > 0 else None
+    lib = _lib("latent")
+    _check(lib, lib.vapi_latent_prepare(_p(down), ctypes.c_longlong(down.stride(0)), _p(q_weight), _p(kv_weight),
+                                        ctypes.c_float(eps), _p(cos), _p(sin), int(rot), _p(cq), _p(cache_layer),
+                                        _DT[out_dtype], _p(slot_mapping), n, int(q_rank), int(kv_rank), int(rot_dim),
+                                        int(page_size), num_pages, _p(status), _stream()))
+    return cq
+
+
+def latent_rotate_q(q: torch.Tensor, qfull: torch.Tensor, heads: int, dim: int, rot_dim: int, kv_rank: int,
+                    cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], rot: int) -> None:
+    """The rotated part of every head's query, ``q`` [n, heads * (dim + rot_dim)], rotated by the token's position
+    into the last ``rot_dim`` columns of ``qfull`` [n, heads, kv_rank + rot_dim] (contiguous)."""
+    _cuda(q, qfull, cos, sin)
+    _f32(cos, "cos")
+    _f32(sin, "sin")
+    _contig(qfull, "attention queries")
+    n = q.shape[0]
+    if q.dtype != qfull.dtype or q.stride(1) != 1 or qfull.numel() != n * heads * (kv_rank + rot_dim):
+        raise KernelError("queries of one dtype, [n, heads * (dim + rot_dim)] and [n, heads, kv_rank + rot_dim]")
+    if rot > 0 and (cos is None or sin is None or cos.shape != (n, rot // 2) or sin.shape != cos.shape):
+        raise KernelError("cos/sin must be [n, rot/2]")
+    lib = _lib("latent")
+    _check(lib, lib.vapi_latent_rotate_q(_p(q), ctypes.c_longlong(q.stride(0)), _p(cos), _p(sin), int(rot), _p(qfull), _dt(q),
+                                         n, int(heads), int(dim), int(rot_dim), int(kv_rank), _stream()))
+
+
 def gated_group_rmsnorm(y: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, eps: float, group: int,
                         gate_first: bool, out_dtype: torch.dtype, gate: str = "silu") -> torch.Tensor:
     """RMS norm over equal groups of ``group`` columns of the float32 rows ``y`` [n, width] with a
@@ -1117,13 +1218,21 @@ def qk_norm_rope_write_split(qkv: torch.Tensor, nh: int, nkv: int, dk: int, dv: 
                              q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
                              cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], rot: int, interleaved: bool,
                              cache_layer: Optional[torch.Tensor], page_size: int, slot_mapping: Optional[torch.Tensor],
-                             status: Optional[torch.Tensor] = None, whole: bool = False) -> None:
+                             status: Optional[torch.Tensor] = None, whole: bool = False,
+                             positions: Optional[torch.Tensor] = None, q_temp: Optional[Tuple[float, int]] = None) -> None:
     """:func:`qk_norm_rope_write` for keys of width ``dk`` and values of width ``dv``: ``qkv`` [n, >=
     (nh+nkv)*dk + nkv*dv] holds q heads, k heads, v heads (columns beyond them are left alone);
     the rotation pairs (2i, 2i+1) when ``interleaved``, else (i, i + rot/2); ``cache_layer`` is the
     call site's pages, flat [pages, page_size * nkv * (dk + dv)]: keys [nkv, page_size, dk], then
     values [nkv, page_size, dv].  ``whole``: the RMS norms run over a token's whole q (and whole k), all heads at
-    once, with weights of ``nh * dk`` and ``nkv * dk`` elements, instead of per head with weights of ``dk``."""
+    once, with weights of ``nh * dk`` and ``nkv * dk`` elements, instead of per head with weights of ``dk``.
+    ``q_temp`` = (coef, every) with ``positions`` [n]: the query at position p is multiplied by
+    ``1 + coef * ln(floor((p + 1) / every) + 1)`` (float32) before it is stored."""
+    qt_coef, qt_every = (float(q_temp[0]), int(q_temp[1])) if q_temp is not None else (0.0, 0)
+    if q_temp is not None and (qt_every < 1 or positions is None or positions.numel() != qkv.shape[0]):
+        raise KernelError("a query temperature needs `every` >= 1 and one position per token")
+    _cuda(positions)
+    _i32(positions, "positions")
     for wt, heads, what in ((q_weight, nh, "q"), (k_weight, nkv, "k")):
         if wt is not None and wt.numel() != (heads * dk if whole else dk):
             raise KernelError(f"the {what} norm's weight has {wt.numel()} elements")
@@ -1148,7 +1257,7 @@ def qk_norm_rope_write_split(qkv: torch.Tensor, nh: int, nkv: int, dk: int, dv: 
     _check(lib, lib.vapi_qk_norm_rope_write_split(
         _p(qkv), ctypes.c_longlong(qkv.stride(0)), _dt(qkv), _p(q_weight), _p(k_weight), ctypes.c_float(eps), _p(cos),
         _p(sin), int(rot), 1 if interleaved else 0, _p(cache_layer), _p(slot_mapping), n, nh, nkv, dk, dv, int(page_size),
-        num_pages, 1 if whole else 0, _p(status), _stream()))
+        num_pages, 1 if whole else 0, _p(status), _stream(), _p(positions), ctypes.c_float(qt_coef), qt_every))
 
 
 def masked_attention_splits(num_seqs: int, max_q: int, max_k: int, nh: int, nkv: int) -> int:
@@ -1166,13 +1275,16 @@ def masked_attention(q: torch.Tensor, q_row_stride: int, cache_layer: torch.Tens
                      block_table: torch.Tensor, cu_q: torch.Tensor, seqlens_k: torch.Tensor, n: int, num_seqs: int,
                      max_q: int, max_k: int, nh: int, nkv: int, dk: int, dv: int, scale: float, *, window: int = 0,
                      chunk: int = 0, sinks: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
-                     splits: Optional[int] = None, status: Optional[torch.Tensor] = None, keep: int = 0) -> torch.Tensor:
+                     splits: Optional[int] = None, status: Optional[torch.Tensor] = None, keep: int = 0,
+                     shared_kv: bool = False) -> torch.Tensor:
     """Causal GQA attention of a mixed batch over the paged cache for keys of width ``dk`` and values
     of width ``dv``; returns [n, nh*dv].  A query at position p sees key i iff i <= p, (i > p - window or
     i < keep) (``window`` > 0; ``keep``: the first tokens of a sequence, which a window never leaves behind)
     and i // chunk == p // chunk (``chunk`` > 0).  ``sinks`` [nh] float32 adds
     exp(sink_h) to head h's softmax denominator; ``gate`` [n, nh] (any row stride) multiplies head
-    h's output by sigmoid(gate).  ``cache_layer``: flat pages as for :func:`qk_norm_rope_write_split`."""
+    h's output by sigmoid(gate).  ``cache_layer``: flat pages as for :func:`qk_norm_rope_write_split`.
+    ``shared_kv``: a page holds key rows alone, [nkv, page_size, dk], and a key's value is the first ``dv`` elements
+    of its own row (latent attention)."""
     _cuda(q, cache_layer, block_table, cu_q, seqlens_k, sinks, gate)
     _i32(block_table, "block table")
     _i32(cu_q, "cu_q")
@@ -1181,8 +1293,9 @@ def masked_attention(q: torch.Tensor, q_row_stride: int, cache_layer: torch.Tens
     _contig(cache_layer, "cache layer")
     if cache_layer.dtype != q.dtype:
         raise KernelError("q and the cache must have one dtype")
-    if cache_layer.dim() != 2 or cache_layer.shape[1] != page_size * nkv * (dk + dv):
-        raise KernelError(f"cache layer {tuple(cache_layer.shape)} does not fit pages of {page_size} x {nkv} x ({dk} + {dv})")
+    if cache_layer.dim() != 2 or cache_layer.shape[1] != page_size * nkv * (dk if shared_kv else dk + dv):
+        raise KernelError(f"cache layer {tuple(cache_layer.shape)} does not fit pages of {page_size} x {nkv} x "
+                          f"({dk}{'' if shared_kv else f' + {dv}'})")
     if block_table.dim() != 2 or block_table.stride(1) != 1:
         raise KernelError("block table must be [S, width] with unit inner stride")
     if sinks is not None and sinks.numel() != nh:
@@ -1209,8 +1322,8 @@ def masked_attention(q: torch.Tensor, q_row_stride: int, cache_layer: torch.Tens
         _p(q), ctypes.c_longlong(q_row_stride), _p(cache_layer), _dt(q), _p(block_table), block_table.stride(0), _p(cu_q),
         _p(seqlens_k), _p(sinks), _p(gate), ctypes.c_longlong(gate_stride), _p(out), _p(part_o), _p(part_ml), n, num_seqs,
         max_q, nh, nkv, dk, dv, int(page_size), cache_layer.shape[0], ctypes.c_float(scale), int(window), int(chunk),
-        int(splits), _p(status), _stream(), int(keep)),
-        2 if splits > 1 or (q.dtype == torch.bfloat16 and dk == dv == 64 and max_q >= 64 and num_seqs > 1) else 1)
+        int(splits), _p(status), _stream(), int(keep), 1 if shared_kv else 0),
+        2 if splits > 1 or (not shared_kv and q.dtype == torch.bfloat16 and dk == dv == 64 and max_q >= 64 and num_seqs > 1) else 1)
     return out
 
 
@@ -1547,14 +1660,47 @@ def moe_route(h: torch.Tensor, router: torch.Tensor, correction: Optional[torch.
     return ids, wts, (offsets, pair_of, ntiles, tile_expert, tile_row0)
 
 
+def moe_table_route(tokens: torch.Tensor, table: torch.Tensor, experts: int, status: Optional[torch.Tensor] = None):
+    """A mixture of experts without a router: row ``tokens[t]`` of ``table`` [vocab, top] int32 names token t's
+    experts, each with weight ``1 / top``.  Returns what :func:`moe_route` returns."""
+    _cuda(tokens, table)
+    _i32(tokens, "tokens")
+    _i32(table, "expert table")
+    _contig(table, "expert table")
+    if table.dim() != 2:
+        raise KernelError("the expert table must be [vocab, top]")
+    n, (vocab, top) = tokens.numel(), table.shape
+    dev = tokens.device
+    pairs = n * top
+    ids = torch.empty((n, top), dtype=torch.int32, device=dev)
+    wts = torch.empty((n, top), dtype=torch.float32, device=dev)
+    max_tiles = pairs // 64 + max(experts, 1)
+    sizes = [pairs, experts + 1, pairs, 1, max_tiles, max_tiles]
+    book = torch.empty((sum(sizes),), dtype=torch.int32, device=dev)
+    parts, at = [], 0
+    for z in sizes:
+        parts.append(book[at:at + z])
+        at += z
+    ranks, offsets, pair_of, ntiles, tile_expert, tile_row0 = parts
+    lib = _lib("moe")
+    _check(lib, lib.vapi_moe_table_route(_p(tokens), _p(table), int(vocab), _p(ids), _p(wts), _p(ranks), _p(offsets),
+                                         _p(pair_of), _p(ntiles), _p(tile_expert), _p(tile_row0), n, int(experts), int(top),
+                                         _p(status), _stream()), 2)
+    return ids, wts, (offsets, pair_of, ntiles, tile_expert, tile_row0)
+
+
 def moe_experts(h: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, plan, w_up: Optional[torch.Tensor],
-                w_down: Optional[torch.Tensor], shared: Optional[torch.Tensor] = None, gated: bool = False) -> torch.Tensor:
+                w_down: Optional[torch.Tensor], shared: Optional[torch.Tensor] = None, gated: bool = False,
+                act: Tuple[float, float, float] = (0.0, 1.0, 0.0)) -> torch.Tensor:
     """The weighted sum of the chosen experts' outputs for ``h`` [n, W]: expert e is ``W_down[e] relu(W_up[e] h)^2``
     with ``w_up`` [experts, ff, W] and ``w_down`` [experts, W, ff] of h's dtype; a choice >= experts is an identity
     expert (its output is h); ``shared`` [n, W] is added when given.  ``ids``, ``wts``, ``plan``: from
     :func:`moe_route`.  ``gated``: expert e is ``W_down[e] (silu(W_gate[e] h) * (W_up[e] h))`` and ``w_up`` is
-    [experts, 2 * ff, W] with rows alternating gate_0, up_0, gate_1, up_1, ..."""
+    [experts, 2 * ff, W] with rows alternating gate_0, up_0, gate_1, up_1, ...  ``act`` = (limit, alpha, shift)
+    generalises the gated form to ``g' * sigmoid(alpha g') * (u' + shift)`` with ``g' = min(g, limit)`` and
+    ``u' = clamp(u, -limit, limit)`` when ``limit`` > 0 (the default is SiLU gating)."""
     _cuda(h, ids, wts, w_up, w_down, shared)
+    limit, alpha, shift = (ctypes.c_float(float(v)) for v in act)
     _contig(h, "expert input")
     n, W = h.shape
     top = ids.shape[1]
@@ -1574,10 +1720,10 @@ def moe_experts(h: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, plan, w_u
         y = torch.empty((pairs, W), dtype=torch.float32, device=h.device)
         _check(lib, lib.vapi_moe_grouped(_p(h), ctypes.c_longlong(h.stride(0)), _p(w_up), _dt(h), _p(ntiles), _p(tile_expert),
                                          _p(tile_row0), _p(offsets), _p(pair_of), _p(wts), _p(hid), pairs, experts, rows_up, W,
-                                         top, 2 if gated else 0, _stream()))
+                                         top, 2 if gated else 0, _stream(), limit, alpha, shift))
         _check(lib, lib.vapi_moe_grouped(_p(hid), ctypes.c_longlong(ff), _p(w_down), _dt(h), _p(ntiles), _p(tile_expert),
                                          _p(tile_row0), _p(offsets), _p(pair_of), _p(wts), _p(y), pairs, experts, W, ff,
-                                         top, 1, _stream()))
+                                         top, 1, _stream(), limit, alpha, shift))
     if shared is not None:
         _contig(shared, "shared expert output")
         if shared.shape != h.shape or shared.dtype != h.dtype:

@@ -32,7 +32,10 @@ class GQAttention(Mixer):
     ``out_gate`` (the concatenated heads times ``sigmoid(W_g x)`` element by element, a gate as wide as the
     heads' output, its rows riding on the fused projection too), ``rope_layout`` ("half": pairs (i, i + rot/2);
     "interleaved": pairs (2i, 2i+1)) and ``weight_suffix`` (what follows a projection's name in the
-    checkpoint).  Any of these but the last sends the mixer to the general kernels
+    checkpoint), ``bias_suffix`` (what follows it for its bias), ``fixed_sink`` (a sink whose score is this number
+    for every head, with no tensor: 0.0 puts a plain one into the denominator) and ``q_temp`` = (coef, every) (the
+    query at position p is multiplied by ``1 + coef * ln(floor((p + 1) / every) + 1)``).  Any of these but the
+    suffixes sends the mixer to the general kernels
     (``ops.qk_norm_rope_write_split``, ``ops.masked_attention``); the plain form keeps the
     specialised ones.
     """
@@ -43,7 +46,8 @@ class GQAttention(Mixer):
                  scale: Optional[float] = None, names: Optional[Dict[str, str]] = None,
                  v_head_dim: Optional[int] = None, chunk: int = 0, sink: bool = False, head_gate: bool = False,
                  rope_layout: str = "half", weight_suffix: str = ".weight", keep_first: int = 0, out_gate: bool = False,
-                 qk_norm: str = "head"):
+                 qk_norm: str = "head", bias_suffix: str = ".bias", fixed_sink: Optional[float] = None,
+                 q_temp: Optional[Any] = None):
         if n_heads <= 0 or n_kv_heads <= 0 or n_heads % n_kv_heads:
             raise ValueError(f"{n_heads} heads are not a multiple of {n_kv_heads} kv heads")
         if rope_layout not in ("half", "interleaved"):
@@ -57,14 +61,21 @@ class GQAttention(Mixer):
         self.whole_norm = qk_norm == "projection" and qk_norm_eps is not None
         if self.head_gate and self.out_gate:
             raise ValueError("a gate per head and a gate per element exclude one another")
+        if fixed_sink is not None and self.sink:
+            raise ValueError("a learned sink and a fixed one exclude one another")
+        self.fixed_sink = float(fixed_sink) if fixed_sink is not None else None
+        self.q_temp = (float(q_temp[0]), int(q_temp[1])) if q_temp is not None else None
+        if self.q_temp is not None and (self.q_temp[1] < 1 or self.whole_norm):
+            raise ValueError("a query temperature needs `every` >= 1 and q/k norms per head")
         self.general = bool(self.dv != int(head_dim) or self.chunk > 0 or self.sink or self.head_gate or self.interleaved
-                            or self.keep_first > 0 or self.out_gate or self.whole_norm)
+                            or self.keep_first > 0 or self.out_gate or self.whole_norm or self.fixed_sink is not None
+                            or self.q_temp is not None)
         if self.general:
             if head_dim % 4 or self.dv % 4 or not (4 <= head_dim <= 256 and 4 <= self.dv <= 256):
                 raise ValueError(f"head sizes {head_dim} / {self.dv} must be multiples of 4 in 4..256")
         elif head_dim % 16 or not 16 <= head_dim <= 256:
             raise ValueError(f"head_dim {head_dim} must be a multiple of 16 in 16..256")
-        self.sfx = weight_suffix
+        self.sfx, self.bsfx = weight_suffix, bias_suffix
         self.hidden, self.nh, self.nkv, self.d = int(hidden), int(n_heads), int(n_kv_heads), int(head_dim)
         self.qk_norm_eps = qk_norm_eps
         self.pos = pos
@@ -95,10 +106,11 @@ class GQAttention(Mixer):
         if self.sink:
             specs.append(TensorSpec(f"{prefix}{n['sink']}", (nh,), role="vector", init="normal"))
         if self.bias:
-            specs += [TensorSpec(f"{prefix}{n['q']}.bias", (nh * d,), role="vector"),
-                      TensorSpec(f"{prefix}{n['k']}.bias", (nkv * d,), role="vector"),
-                      TensorSpec(f"{prefix}{n['v']}.bias", (nkv * self.dv,), role="vector"),
-                      TensorSpec(f"{prefix}{n['o']}.bias", (h,), role="vector")]
+            b = self.bsfx
+            specs += [TensorSpec(f"{prefix}{n['q']}{b}", (nh * d,), role="vector"),
+                      TensorSpec(f"{prefix}{n['k']}{b}", (nkv * d,), role="vector"),
+                      TensorSpec(f"{prefix}{n['v']}{b}", (nkv * self.dv,), role="vector"),
+                      TensorSpec(f"{prefix}{n['o']}{b}", (h,), role="vector")]
         if self.qk_norm_eps is not None:
             specs += [TensorSpec(f"{prefix}{n['q_norm']}{x}", (nh * d if self.whole_norm else d,), role="vector", init="ones"),
                       TensorSpec(f"{prefix}{n['k_norm']}{x}", (nkv * d if self.whole_norm else d,), role="vector", init="ones")]
@@ -119,11 +131,13 @@ class GQAttention(Mixer):
         self.w_o = tensors[f"{prefix}{n['o']}{x}"].contiguous()
         if self.sink:
             self.sinks = tensors[f"{prefix}{n['sink']}"].contiguous()
+        elif self.fixed_sink is not None:
+            self.sinks = torch.full((self.nh,), self.fixed_sink, dtype=torch.float32, device=self.w_o.device)
         if self.bias:
-            self.b_qkv = torch.cat([tensors[f"{prefix}{n[r]}.bias"] for r in ("q", "k", "v")], 0).contiguous()
+            self.b_qkv = torch.cat([tensors[f"{prefix}{n[r]}{self.bsfx}"] for r in ("q", "k", "v")], 0).contiguous()
             if self.b_qkv.numel() < self.w_qkv.shape[0]:       # the gate's rows and the padding have no bias
                 self.b_qkv = torch.cat([self.b_qkv, self.b_qkv.new_zeros(self.w_qkv.shape[0] - self.b_qkv.numel())])
-            self.b_o = tensors[f"{prefix}{n['o']}.bias"].contiguous()
+            self.b_o = tensors[f"{prefix}{n['o']}{self.bsfx}"].contiguous()
         if self.qk_norm_eps is not None:
             self.q_w = tensors[f"{prefix}{n['q_norm']}{x}"].contiguous()
             self.k_w = tensors[f"{prefix}{n['k_norm']}{x}"].contiguous()
@@ -193,7 +207,8 @@ class GQAttention(Mixer):
         ops.qk_norm_rope_write_split(qkv, nh, nkv, d, dv, self.q_w, self.k_w,
                                      self.qk_norm_eps if self.qk_norm_eps is not None else 0.0, cos, sin, self.rot_dim,
                                      self.interleaved, pages if cache.write else None, page_size, grp.slot_mapping,
-                                     ctx.status, whole=self.whole_norm)
+                                     ctx.status, whole=self.whole_norm,
+                                     positions=ctx.positions if self.q_temp is not None else None, q_temp=self.q_temp)
         gate = None
         if self.head_gate:
             off = (nh + nkv) * d + nkv * dv

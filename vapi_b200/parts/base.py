@@ -181,6 +181,19 @@ class PostNormed:
     mult: float = 1.0
 
 
+@dataclass
+class ScaledPair:
+    """The outputs of two sublayers that ran side by side on one normed input, still to be scaled column by column
+    and added into the residual stream: ``x <- x + scale_a * a + scale_b * b`` (layer scale; ``b`` None: the block
+    has one sublayer; a scale None counts as one).  The norm that reads the stream next does the update while it
+    reads the row (:meth:`Norm.apply` accepts it wherever it accepts a delta)."""
+
+    a: torch.Tensor
+    scale_a: Optional[torch.Tensor]
+    b: Optional[torch.Tensor] = None
+    scale_b: Optional[torch.Tensor] = None
+
+
 # --------------------------------------------------------------------------------------
 # the parts
 

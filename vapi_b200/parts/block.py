@@ -5,7 +5,7 @@ from typing import Any, Callable, Dict, List, Optional
 
 import torch
 
-from .base import CacheView, FeedForward, Mixer, Norm, Part, PostNormed, StreamState, TensorSpec
+from .base import CacheView, FeedForward, Mixer, Norm, Part, PostNormed, ScaledPair, StreamState, TensorSpec
 
 BLOCKS: Dict[str, Callable[..., "Part"]] = {}
 
@@ -139,5 +139,54 @@ class SandwichBlock(Part):
         return PostNormed(self.ffn.forward(f, ctx), self.ffn_post.weight, self.ffn_post.eps, self.mult)
 
 
+class ParallelBlock(Part):
+    """One norm, and both sublayers read its output: ``h = norm(x)``; ``x <- x + s_m * mixer(h) + s_f * ffn(h)``.
+
+    ``s_m`` and ``s_f`` are vectors over the width (layer scale), named by ``scales = (mixer's, feed-forward's)``
+    under the block's prefix; a name None means no scale.  ``ffn`` may be None: the block then has the mixer alone.
+    Neither output is added by a kernel of its own: the block hands both on as a :class:`ScaledPair`, and the norm
+    that reads the stream next (the next block's, or the model's final norm) scales and adds them while it reads
+    the row.  ``sub`` gives the checkpoint sub-prefix of ``norm``, ``mixer`` and ``ffn``.
+    """
+
+    def __init__(self, norm: Norm, mixer: Mixer, ffn: Optional[FeedForward], sub: Dict[str, str],
+                 scales=(None, None), hidden: Optional[int] = None):
+        self.norm, self.mixer, self.ffn, self.sub = norm, mixer, ffn, dict(sub)
+        self.scale_names = (scales[0], scales[1] if ffn is not None else None)
+        self.hidden = int(hidden) if hidden is not None else int(getattr(norm, "dim", 0))
+        if any(self.scale_names) and self.hidden <= 0:
+            raise ValueError("a layer scale needs the width")
+        self.s_m = self.s_f = None
+
+    def _parts(self):
+        out = [("norm", self.norm), ("mixer", self.mixer)]
+        if self.ffn is not None:
+            out.append(("ffn", self.ffn))
+        return out
+
+    def tensor_specs(self, prefix: str) -> List[TensorSpec]:
+        out: List[TensorSpec] = []
+        for key, part in self._parts():
+            out += part.tensor_specs(prefix + self.sub.get(key, ""))
+        out += [TensorSpec(prefix + name, (self.hidden,), role="vector", init="ones") for name in self.scale_names if name]
+        return out
+
+    def bind(self, tensors, prefix, dtype):
+        for key, part in self._parts():
+            part.bind(tensors, prefix + self.sub.get(key, ""), dtype)
+        self.s_m = tensors[prefix + self.scale_names[0]].contiguous() if self.scale_names[0] else None
+        self.s_f = tensors[prefix + self.scale_names[1]].contiguous() if self.scale_names[1] else None
+
+    def first_norm(self) -> Norm:
+        return self.norm
+
+    def forward(self, x: torch.Tensor, delta, ctx: Any, cache: CacheView) -> ScaledPair:
+        h = self.norm.apply(x, delta, ctx.dtype)
+        a = self.mixer.forward(h, ctx, cache)
+        b = self.ffn.forward(h, ctx) if self.ffn is not None else None
+        return ScaledPair(a, self.s_m, b, self.s_f)
+
+
 register_block("prenorm", PreNormBlock)
+register_block("parallel", ParallelBlock)
 register_block("sandwich", SandwichBlock)

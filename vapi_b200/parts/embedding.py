@@ -15,8 +15,10 @@ class TokenEmbedding(Part):
 
     def __init__(self, vocab: int, hidden: int, name: str = "model.embed_tokens.weight", *,
                  sinusoid_base: Optional[float] = None, streams: Optional[int] = None,
-                 position_table: Optional[str] = None, positions: int = 0):
+                 position_table: Optional[str] = None, positions: int = 0, scale: float = 1.0):
         self.vocab, self.hidden, self.name = int(vocab), int(hidden), name
+        #: every row is multiplied by this number (a float32 product) on its way into the stream
+        self.scale = float(scale)
         #: with ``sinusoid_base`` a position vector is added: entry 2i is sin(p * base^(-2i/hidden)), entry
         #: 2i+1 the cosine of the same angle (positions and angles in float32)
         self.sinusoid_base = float(sinusoid_base) if sinusoid_base is not None else None
@@ -48,12 +50,12 @@ class TokenEmbedding(Part):
     def forward(self, ctx: Any, next_weight: Optional[torch.Tensor] = None):
         """The stream; with ``next_weight`` also what a deferred norm needs: ``(x, ss, xw)``."""
         if self.sinusoid_base is not None or self.streams is not None or self.pos_rows is not None:
-            if next_weight is not None:
-                raise ValueError("an embedding with positions or several streams has no deferred-norm form")
+            if next_weight is not None or self.scale != 1.0:
+                raise ValueError("an embedding with positions or several streams has no deferred-norm form and no scale")
             x = ops.embed_sinusoid(self.table, ctx.tokens, ctx.positions, self.freq, self.streams or 1, ctx.status,
                                    pos_table=self.pos_rows)
             return x if self.streams is not None else x.view(x.shape[0], self.hidden)
-        return ops.embed(self.table, ctx.tokens, ctx.status, next_weight)
+        return ops.embed(self.table, ctx.tokens, ctx.status, next_weight, self.scale)
 
 
 class OutputHead(Part):

@@ -6,7 +6,7 @@ from typing import Dict, List, Optional
 import torch
 
 from .. import ops
-from .base import Norm, NormedStream, PostNormed, TensorSpec, register_norm
+from .base import Norm, NormedStream, PostNormed, ScaledPair, TensorSpec, register_norm
 
 
 def _raw_branches(y):
@@ -43,6 +43,8 @@ class RMSNorm(Norm):
             y, branches = _raw_branches(delta.y)
             return ops.postnorm_add_rmsnorm(x, y, delta.weight, delta.eps, delta.mult, self.weight, self.eps,
                                             dtype, rows, branches=branches)
+        if isinstance(delta, ScaledPair):
+            return ops.scaled_add_rmsnorm(x, delta.a, delta.scale_a, delta.b, delta.scale_b, self.weight, self.eps, dtype, rows)
         return ops.add_rmsnorm(x, delta, self.weight, self.eps, dtype, rows)
 
     def stream_weight(self):

@@ -39,7 +39,12 @@ def random_tensors(plan, seed: int, std: float = 0.02, norm_init: str = "ones",
                              f"before random weights can be drawn")
         g = _gen(seed, spec.name, dev)
         if spec.role == "table":
-            out[spec.name] = torch.zeros(spec.shape, dtype=torch.int32, device=dev)
+            if spec.init.startswith("distinct:"):          # rows of distinct indices below the given number
+                below = int(spec.init.split(":", 1)[1])
+                order = torch.rand((spec.shape[0], below), generator=g, dtype=torch.float32, device=dev).argsort(dim=1)
+                out[spec.name] = order[:, :spec.shape[1]].to(torch.int32).contiguous()
+            else:
+                out[spec.name] = torch.zeros(spec.shape, dtype=torch.int32, device=dev)
             continue
         if spec.init == "ones":
             t = torch.ones(spec.shape, dtype=torch.float32, device=dev)

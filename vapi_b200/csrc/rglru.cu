@@ -23,6 +23,10 @@ using namespace vapi;
 
 __device__ __forceinline__ float rg_sigmoid(float z) { return 1.f / (1.f + expf(-z)); }
 __device__ __forceinline__ float rg_softplus(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+// a = exp(log a) for log a <= 0.  What the recurrence feels of a slow decay is 1 - a, so close to one a must be the
+// float nearest to the true value: expm1f is exact to an ulp of the small number, and the sum with one rounds once.
+// (expf alone may be two ulps of a off, which at a = 0.999 is an error of a part in ten thousand in the decay.)
+__device__ __forceinline__ float rg_decay(float log_a) { return log_a > -0.5f ? 1.f + expm1f(log_a) : expf(log_a); }
 __device__ __forceinline__ float rg_gelu_tanh(float z) {
     return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
@@ -94,7 +98,7 @@ rglru_gates_kernel(const T* __restrict__ u, long long u_stride, const T* __restr
             const float r = rg_sigmoid(acc_a[i][j] + ba[c]);
             const float ig = rg_sigmoid(acc_i[i][j] + bi[c]);
             const float log_a = -decay_c * r * rg_softplus(lam[c]);
-            const float a = expf(log_a);
+            const float a = rg_decay(log_a);
             const float mult = sqrtf(fmaxf(-expm1f(2.f * log_a), 0.f));        // sqrt(1 - a^2), exact near a = 1
             const float uv = to_f32(u[(size_t)t * u_stride + c]);
             a_out[(size_t)t * channels + c] = a;
@@ -158,7 +162,7 @@ rglru_gates_mma_kernel(const __nv_bfloat16* __restrict__ u, long long u_stride, 
         const float log_a = -r * sp;
         const float mult = sqrtf(fmaxf(-expm1f(2.f * log_a), 0.f));
         const float uv = __bfloat162float(u[(size_t)tok * u_stride + c]);
-        a_out[(size_t)tok * channels + c] = expf(log_a);
+        a_out[(size_t)tok * channels + c] = rg_decay(log_a);
         g_out[(size_t)tok * channels + c] = mult * ig * uv;
     }
 }

@@ -16,8 +16,8 @@ def _f(t):
     return t.to(torch.float32)
 
 
-def embed(table, tokens, status=None, next_weight=None):
-    out = _f(table[tokens.long()])
+def embed(table, tokens, status=None, next_weight=None, scale=1.0):
+    out = _f(table[tokens.long()]) * torch.tensor(scale, dtype=torch.float32)
     if next_weight is None:
         return out
     return out, (out ** 2).sum(1)[None, :], (out * next_weight).to(torch.bfloat16)
@@ -301,6 +301,70 @@ def postnorm_add_rmsnorm(x, y, post_weight, post_eps, mult, weight, eps, out_dty
     return (src * torch.rsqrt(src.pow(2).mean(-1, keepdim=True) + eps) * weight).to(out_dtype)
 
 
+def scaled_add_rmsnorm(x, y1, s1, y2, s2, weight, eps, out_dtype, rows=None, copy=False, out=None):
+    """x += s1 * y1 + s2 * y2 (a missing scale counts as one); out = rms(x) * weight, or x itself with `copy`; for `rows`
+    only those rows and x untouched.  A given `out` is filled and returned."""
+    add = None
+    for y, sc in ((y1, s1), (y2, s2)):
+        if y is not None:
+            term = _f(y) * (sc if sc is not None else 1.0)
+            add = term if add is None else add + term
+    if rows is None:
+        if add is not None:
+            x += add
+        src = x
+    else:
+        src = x[rows.long()] + (add[rows.long()] if add is not None else 0.0)
+    if weight is None and not copy:
+        return None
+    res = src if weight is None else src * torch.rsqrt(src.pow(2).mean(-1, keepdim=True) + eps) * weight
+    if out is not None:
+        out.copy_(res.to(out_dtype))
+        return out
+    return res.to(out_dtype)
+
+
+def _rotate_half(v, cos_t, sin_t, rot):
+    half = rot // 2
+    r = v.clone()
+    for i in range(half):
+        r[..., i] = v[..., i] * cos_t[i] - v[..., i + half] * sin_t[i]
+        r[..., i + half] = v[..., i + half] * cos_t[i] + v[..., i] * sin_t[i]
+    return r
+
+
+def latent_prepare(down, q_rank, kv_rank, rot_dim, q_weight, kv_weight, eps, cos, sin, rot, cache_layer, page_size,
+                   slot_mapping, out_dtype, status=None):
+    """down [n, q_rank | kv_rank | rot_dim] float32: the query latent normed; latent normed | key part rotated, into the page."""
+    n = down.shape[0]
+    cq = None
+    if q_rank > 0:
+        a = down[:, :q_rank]
+        cq = (a * torch.rsqrt(a.pow(2).mean(-1, keepdim=True) + eps) * q_weight).to(out_dtype)
+    if cache_layer is not None:
+        width = kv_rank + rot_dim
+        for t in range(n):
+            c = down[t, q_rank:q_rank + kv_rank]
+            c = c * torch.rsqrt(c.pow(2).mean() + eps) * kv_weight
+            kr = down[t, q_rank + kv_rank:q_rank + width]
+            if rot > 0:
+                kr = _rotate_half(kr, cos[t], sin[t], rot)
+            slot = int(slot_mapping[t])
+            pg, off = slot // page_size, slot % page_size
+            cache_layer[pg, off * width:(off + 1) * width] = torch.cat([c, kr]).to(cache_layer.dtype)
+    return cq
+
+
+def latent_rotate_q(q, qfull, heads, dim, rot_dim, kv_rank, cos, sin, rot):
+    n = q.shape[0]
+    q3 = _f(q).view(n, heads, dim + rot_dim)
+    for t in range(n):
+        part = q3[t, :, dim:]
+        if rot > 0:
+            part = _rotate_half(part, cos[t], sin[t], rot)
+        qfull[t, :, kv_rank:] = part.to(qfull.dtype)
+
+
 def gated_group_rmsnorm(y, z, weight, eps, group, gate_first, out_dtype, gate="silu"):
     n, width = y.shape
     zf = _f(z)
@@ -323,9 +387,12 @@ def rope_cos_sin_scaled(positions, freq, mult):
 
 
 def qk_norm_rope_write_split(qkv, nh, nkv, dk, dv, q_weight, k_weight, eps, cos, sin, rot, interleaved, cache_layer,
-                             page_size, slot_mapping, status=None, whole=False):
+                             page_size, slot_mapping, status=None, whole=False, positions=None, q_temp=None):
     n = qkv.shape[0]
     for t in range(n):
+        q_mult = 1.0
+        if q_temp is not None:      # the query at position p times 1 + coef * ln(floor((p + 1) / every) + 1)
+            q_mult = 1.0 + q_temp[0] * torch.log(torch.tensor(float((int(positions[t]) + 1) // q_temp[1] + 1), dtype=torch.float32))
         if whole:
             inv_q = torch.rsqrt(_f(qkv[t, :nh * dk]).pow(2).mean() + eps)
             inv_k = torch.rsqrt(_f(qkv[t, nh * dk:(nh + nkv) * dk]).pow(2).mean() + eps)
@@ -350,7 +417,7 @@ def qk_norm_rope_write_split(qkv, nh, nkv, dk, dv, q_weight, k_weight, eps, cos,
                     r[b] = v[b] * cos[t, i] + v[a] * sin[t, i]
                 v = r
             if is_q:
-                qkv[t, c0:c0 + d] = v.to(qkv.dtype)
+                qkv[t, c0:c0 + d] = (v * q_mult).to(qkv.dtype)
             elif cache_layer is not None:
                 slot = int(slot_mapping[t])
                 pg, off = slot // page_size, slot % page_size
@@ -366,7 +433,9 @@ def masked_attention_splits(num_seqs, max_q, max_k, nh, nkv):
 
 
 def masked_attention(q, q_row_stride, cache_layer, page_size, block_table, cu_q, seqlens_k, n, num_seqs, max_q, max_k,
-                     nh, nkv, dk, dv, scale, *, window=0, chunk=0, sinks=None, gate=None, splits=None, status=None, keep=0):
+                     nh, nkv, dk, dv, scale, *, window=0, chunk=0, sinks=None, gate=None, splits=None, status=None, keep=0,
+                     shared_kv=False):
+    """shared_kv: a page holds key rows alone and a key's value is the first dv elements of its row."""
     rep = nh // nkv
     out = torch.zeros((n, nh * dv), dtype=torch.float32)
     kpart = nkv * page_size * dk
@@ -384,7 +453,10 @@ def masked_attention(q, q_row_stride, cache_layer, page_size, block_table, cu_q,
                 for i in seen:
                     pg, off = int(block_table[s, i // page_size]), i % page_size
                     ks.append(_f(cache_layer[pg, (g * page_size + off) * dk:(g * page_size + off + 1) * dk]))
-                    vs.append(_f(cache_layer[pg, kpart + (g * page_size + off) * dv:kpart + (g * page_size + off + 1) * dv]))
+                    if shared_kv:
+                        vs.append(ks[-1][:dv])
+                    else:
+                        vs.append(_f(cache_layer[pg, kpart + (g * page_size + off) * dv:kpart + (g * page_size + off + 1) * dv]))
                 sc = torch.stack(ks) @ qv * scale
                 mx = sc.max()
                 if sinks is not None:
@@ -603,7 +675,16 @@ def moe_route(h, router, correction, experts, top, groups, keep, bias=None, scor
     return ids, wts, None
 
 
-def moe_experts(h, ids, wts, plan, w_up, w_down, shared=None, gated=False):
+def moe_table_route(tokens, table, experts, status=None):
+    """ids = table[token], each with weight 1 / top; no plan is needed by the restatement of the experts."""
+    ids = table[tokens.long()].to(torch.int32)
+    return ids, torch.full(ids.shape, 1.0 / ids.shape[1], dtype=torch.float32), None
+
+
+def moe_experts(h, ids, wts, plan, w_up, w_down, shared=None, gated=False, act=(0.0, 1.0, 0.0)):
+    """act = (limit, alpha, shift): a gated expert's hidden row is g' * sigmoid(alpha g') * (u' + shift) with g' = min(g, limit)
+    and u' = clamp(u, -limit, limit) when limit > 0."""
+    limit, alpha, shift = act
     n, W = h.shape
     experts = 0 if w_up is None else w_up.shape[0]
     out = torch.zeros((n, W), dtype=torch.float32)
@@ -613,7 +694,10 @@ def moe_experts(h, ids, wts, plan, w_up, w_down, shared=None, gated=False):
                 out[t] += g * _f(h[t])
             elif gated:
                 gu = _f(w_up[e]) @ _f(h[t])
-                hid = (gu[0::2] / (1.0 + torch.exp(-gu[0::2])) * gu[1::2]).to(h.dtype)
+                gg, uu = gu[0::2], gu[1::2]
+                if limit > 0:
+                    gg, uu = torch.clamp(gg, max=limit), torch.clamp(uu, min=-limit, max=limit)
+                hid = (gg / (1.0 + torch.exp(-alpha * gg)) * (uu + shift)).to(h.dtype)
                 out[t] += g * (_f(w_down[e]) @ _f(hid))
             else:
                 hid = (torch.relu(_f(w_up[e]) @ _f(h[t])) ** 2).to(h.dtype)
@@ -695,4 +779,5 @@ ALL = ["matrix_memory", "gated_linear_attention", "embed", "resolve_tokens", "sa
        "apply_penalties", "postnorm_add_rmsnorm", "gated_group_rmsnorm", "scale_rows", "rope_cos_sin_scaled",
        "qk_norm_rope_write_split", "masked_attention_splits", "masked_attention", "causal_conv_silu", "gated_delta",
        "state_space", "causal_conv", "embed_sinusoid", "hyper_read_norm", "branch_rmsnorm_mean", "sigmoid_gate", "softcap",
-       "rglru", "relu_squared", "moe_route", "moe_experts"]
+       "rglru", "relu_squared", "moe_route", "moe_experts", "moe_table_route", "scaled_add_rmsnorm", "latent_prepare",
+       "latent_rotate_q"]

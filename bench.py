@@ -200,7 +200,9 @@ OPS = {"embed": "elementwise", "add_residual_ss": "elementwise", "resolve_tokens
        "causal_conv_silu": "recurrent", "gated_delta": "recurrent", "state_space": "recurrent",
        "embed_sinusoid": "hyper", "hyper_read_norm": "hyper", "branch_rmsnorm_mean": "hyper", "sigmoid_gate": "hyper",
        "softcap": "hyper", "causal_conv": "recurrent", "rglru": "rglru", "relu_squared": "moe", "moe_route": "moe",
-       "moe_experts": "moe", "matrix_memory": "linear_memory", "gated_linear_attention": "linear_memory"}
+       "moe_experts": "moe", "matrix_memory": "linear_memory", "gated_linear_attention": "linear_memory",
+       "scaled_add_rmsnorm": "elementwise", "latent_prepare": "latent", "latent_rotate_q": "latent",
+       "latent_attention": "attention_masked", "moe_table_route": "moe", "head_products": "library"}
 
 
 class OpLog:
@@ -807,9 +809,33 @@ def demazen_sizes(name):
     return dz, vukavik_sizes(name)[0], rapolix_sizes(name)[0]
 
 
+def nelosun_sizes(name):
+    """Nelosun layers at the widths of LFM2-<name>: attention with the same heads as the LFM2 stack (keys and values of
+    64, a sink, a gate per head, biases, a query temperature that steps every 1,024 positions); latent attention with
+    as many heads of 64 + 32 (values of 64) over a cached row of 256 + 32 and a query latent of three eighths of the
+    width; a recurrent block as wide as the model in parts of 256 with a convolution of four taps; behind every mixer
+    a mixture of 16 gated experts with clamped activations (a quarter of the LFM2 stack's feed-forward width each, four
+    of them a token, chosen by a table over the token ids); eight layers in one pass of the loop, so that the input
+    product runs once.  Beside it Rapolix (general attention beside the same recurrent block, squared-ReLU experts
+    behind a router) and Demazen (gated experts behind a router) at the same widths."""
+    from vapi_b200.models.lfm2 import Lfm2Config
+    lf = lfm2_sizes(name)
+    W, ff = lf["hidden_size"], Lfm2Config.effective_ff_dim(lf)
+    heads = lf["num_attention_heads"]
+    mlp = {"kind": "moe", "expert": {"ff": ff // 4, "limit": 7.0}, "router": {"experts": 16, "top": 4}}
+    att = {"type": "attention", "mlp": mlp, "mixer": {"heads": heads, "kv_heads": lf["num_key_value_heads"], "dim": 64, "vdim": 64,
+                                                      "scale": 0.125, "q_temp": {"coef": 0.1, "every": 1024}}}
+    lat = {"type": "latent_attention", "mlp": mlp, "mixer": {"heads": heads, "dim": 64, "rot_dim": 32, "vdim": 64, "kv_rank": 256,
+                                                             "q_rank": 3 * W // 8, "scale": 0.1, "rot": {"base": 10000.0, "dims": 32}}}
+    rec = {"type": "rglru", "mlp": mlp, "mixer": {"width": W, "blocks": W // 256, "conv": 4}}
+    ne = {"architecture": "Nelosun", "vocab": lf["vocab_size"], "width": W, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},
+          "loop": {"start": 0, "stop": 8, "times": 1}, "layers": [lat, att, rec, att] * 2}
+    return ne, rapolix_sizes(name)[0], demazen_sizes(name)[0]
+
+
 def mixers(args):
     """``--only mixers``: prefill and decode of eight layers of ``--design`` beside LFM2 layers (Vukavik, Rapolix; Demazen
-    stands beside Vukavik and Rapolix, whose kernels are the nearest to its own)
+    stands beside Vukavik and Rapolix, whose kernels are the nearest to its own, Nelosun beside Rapolix and Demazen)
     of equal width (random weights), and where each model's time goes, kernel family by kernel family."""
     import torch
     from vapi_b200 import ops
@@ -827,6 +853,9 @@ def mixers(args):
     if args.design == "demazen":
         dz, vk, rp = demazen_sizes(args.sizes)
         models = (("demazen", dz), ("vukavik", vk), ("rapolix", rp))
+    elif args.design == "nelosun":
+        ne, rp, dz = nelosun_sizes(args.sizes)
+        models = (("nelosun", ne), ("rapolix", rp), ("demazen", dz))
     else:
         vk, lf = rapolix_sizes(args.sizes) if args.design == "rapolix" else vukavik_sizes(args.sizes)
         models = ((args.design, vk), ("lfm2", lf))
@@ -871,7 +900,8 @@ def mixers(args):
         for blk in runner.plan.layers:
             ffn = getattr(blk, "ffn", None)
             if type(ffn).__name__ == "SparseMoE":
-                mix_flops["moe_experts"] = 2.0 * 2 * ffn.top * ffn.ff * ffn.hidden * T      # as if every choice were an expert
+                # (as if every choice were an expert; a gated expert has three matrices)
+                mix_flops["moe_experts"] = 2.0 * (3 if ffn.gated else 2) * ffn.top * ffn.ff * ffn.hidden * T
                 mix_flops["moe_route"] = 2.0 * (ffn.E + ffn.I) * ffn.hidden * T
         for blk in runner.plan.layers:
           for m in blk.mixer.members():
@@ -881,6 +911,10 @@ def mixers(args):
                 mix_flops["masked_attention" if m.general else "paged_attention"] = 2.0 * m.nh * (m.d + m.dv) * pairs
             elif kind == "RGLRUMixer":
                 mix_flops["rglru"] = 2.0 * 2 * m.C * (m.C // m.B) * T                        # the two gates' products
+            elif kind == "LatentAttention":
+                # a score over the whole cached row, a weighted sum over its latent
+                mix_flops["latent_attention"] = 2.0 * m.H * (2 * m.R + m.r) * T * (T + 1) / 2
+                mix_flops["head_products"] = 2.0 * m.H * m.R * (m.d + m.dv) * T / 2         # two calls a layer: their mean
             elif kind == "GQAttention":
                 span = min(T, m.chunk) if getattr(m, "chunk", 0) else T
                 pairs = (T // span) * span * (span + 1) / 2 + (T % span) * (T % span + 1) / 2
@@ -993,8 +1027,9 @@ def main():
                          "and print what one step's kernels did inside the captured graph, or (mixers) prefill and "
                          "decode of eight Vukavik layers beside eight LFM2 layers of equal width, kernel family by kernel family")
     ap.add_argument("--sizes", default="1.2b", choices=["1.2b", "700m", "2.6b"], help="layer sizes of LFM2-<sizes>")
-    ap.add_argument("--design", default="vukavik", choices=["vukavik", "rapolix", "demazen"],
-                    help="with --only mixers: the architecture whose layers stand beside LFM2's (demazen: beside Vukavik's and Rapolix's)")
+    ap.add_argument("--design", default="vukavik", choices=["vukavik", "rapolix", "demazen", "nelosun"],
+                    help="with --only mixers: the architecture whose layers stand beside LFM2's (demazen: beside Vukavik's and "
+                         "Rapolix's; nelosun: beside Rapolix's and Demazen's)")
     ap.add_argument("--page-size", type=int, default=0, help="tokens per cache page (0: the engine's default)")
     ap.add_argument("--dtype", default="bfloat16", help="bfloat16 (serving) or float32 (the true 32-bit path)")
     ap.add_argument("--no-fp32", action="store_true", help="leave the float32 points out of the default run")

@@ -365,6 +365,22 @@ def latent_rotate_q(q, qfull, heads, dim, rot_dim, kv_rank, cos, sin, rot):
         qfull[t, :, kv_rank:] = part.to(qfull.dtype)
 
 
+def head_products(x, w, out=None):
+    """out[t, h] = x[t, h] @ w[h]"""
+    res = torch.einsum("thk,hkm->thm", _f(x), _f(w)).to(x.dtype).contiguous()
+    if out is None:
+        return res
+    out.copy_(res)
+    return out
+
+
+def latent_attention(q, cache_layer, page_size, block_table, cu_q, seqlens_k, n, num_seqs, max_q, max_k, heads, kv_rank, rot_dim,
+                     scale, *, splits=None, status=None):
+    width = kv_rank + rot_dim
+    return masked_attention(q, heads * width, cache_layer, page_size, block_table, cu_q, seqlens_k, n, num_seqs, max_q, max_k,
+                            heads, 1, width, kv_rank, scale, shared_kv=True)
+
+
 def gated_group_rmsnorm(y, z, weight, eps, group, gate_first, out_dtype, gate="silu"):
     n, width = y.shape
     zf = _f(z)
@@ -780,4 +796,4 @@ ALL = ["matrix_memory", "gated_linear_attention", "embed", "resolve_tokens", "sa
        "qk_norm_rope_write_split", "masked_attention_splits", "masked_attention", "causal_conv_silu", "gated_delta",
        "state_space", "causal_conv", "embed_sinusoid", "hyper_read_norm", "branch_rmsnorm_mean", "sigmoid_gate", "softcap",
        "rglru", "relu_squared", "moe_route", "moe_experts", "moe_table_route", "scaled_add_rmsnorm", "latent_prepare",
-       "latent_rotate_q"]
+       "latent_rotate_q", "head_products", "latent_attention"]

@@ -1166,6 +1166,35 @@ def latent_rotate_q(q: torch.Tensor, qfull: torch.Tensor, heads: int, dim: int, 
                                          n, int(heads), int(dim), int(rot_dim), int(kv_rank), _stream()))
 
 
+def head_products(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One matrix product per head: ``out[t, h, :] = x[t, h, :] @ w[h]`` for ``x`` [n, heads, k] (any row and head
+    strides, unit inner stride), ``w`` [heads, k, m] contiguous and ``out`` [n, heads, m] (likewise strided; made when
+    None).  The library's batched product, as :func:`linear` is the library's product."""
+    _cuda(x, w, out)
+    if x.dim() != 3 or w.dim() != 3 or x.shape[1] != w.shape[0] or x.shape[2] != w.shape[1] or x.dtype != w.dtype or x.stride(2) != 1:
+        raise KernelError(f"head products of {tuple(x.shape)} {x.dtype} with {tuple(w.shape)} {w.dtype}")
+    if out is None:
+        out = torch.empty((x.shape[0], x.shape[1], w.shape[2]), dtype=x.dtype, device=x.device)
+    elif out.shape != (x.shape[0], x.shape[1], w.shape[2]) or out.dtype != x.dtype or out.stride(2) != 1:
+        raise KernelError("the given output must be [n, heads, m] of the inputs' dtype with unit inner stride")
+    torch.bmm(x.transpose(0, 1), w, out=out.transpose(0, 1))
+    return out
+
+
+def latent_attention(q: torch.Tensor, cache_layer: torch.Tensor, page_size: int, block_table: torch.Tensor, cu_q: torch.Tensor,
+                     seqlens_k: torch.Tensor, n: int, num_seqs: int, max_q: int, max_k: int, heads: int, kv_rank: int,
+                     rot_dim: int, scale: float, *, splits: Optional[int] = None,
+                     status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Causal attention of ``heads`` query heads over one cached row per token, ``[latent (kv_rank) | rotated key part
+    (rot_dim)]``: a score is ``scale * q . row`` over the whole row and a head's output is the softmax-weighted sum of
+    the rows' latents, so keys and values are the same memory.  ``q`` [n, heads * (kv_rank + rot_dim)] contiguous;
+    ``cache_layer`` flat pages [pages, page_size * (kv_rank + rot_dim)]; returns [n, heads * kv_rank]."""
+    width = kv_rank + rot_dim
+    _contig(q, "queries")
+    return masked_attention(q, heads * width, cache_layer, page_size, block_table, cu_q, seqlens_k, n, num_seqs, max_q, max_k,
+                            heads, 1, width, kv_rank, scale, splits=splits, status=status, shared_kv=True)
+
+
 def gated_group_rmsnorm(y: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, eps: float, group: int,
                         gate_first: bool, out_dtype: torch.dtype, gate: str = "silu") -> torch.Tensor:
     """RMS norm over equal groups of ``group`` columns of the float32 rows ``y`` [n, width] with a

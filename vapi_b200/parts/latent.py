@@ -98,17 +98,16 @@ class LatentAttention(Mixer):
         if q.dtype != a.dtype:
             q = q.to(a.dtype)
         qfull = torch.empty((n, H, R + r), dtype=a.dtype, device=a.device)
-        torch.bmm(q.view(n, H, d + r)[:, :, :d].transpose(0, 1), self.w_uk, out=qfull[:, :, :R].transpose(0, 1))
+        ops.head_products(q.view(n, H, d + r)[:, :, :d], self.w_uk, qfull[:, :, :R])
         if r:
             ops.latent_rotate_q(q, qfull, H, d, r, R, cos, sin, self.rot)
         splits = grp.splits if getattr(grp, "splits", None) is not None else ctx.attention_splits
         max_k = getattr(grp, "max_k", None) or ctx.max_k
-        o = ops.masked_attention(qfull.view(n, H * (R + r)), H * (R + r), pages, page_size, grp.block_table, ctx.cu_q,
-                                 ctx.seqlens_k, ctx.n, ctx.num_seqs, ctx.max_q, max_k, H, 1, R + r, R, self.scale,
-                                 splits=splits, status=ctx.status, shared_kv=True)          # [n, H * R]
-        y = torch.empty((n, H * dv), dtype=a.dtype, device=a.device)
-        torch.bmm(o.view(n, H, R).transpose(0, 1), self.w_uv, out=y.view(n, H, dv).transpose(0, 1))
-        return ops.linear(y, self.w_o)
+        o = ops.latent_attention(qfull.view(n, H * (R + r)), pages, page_size, grp.block_table, ctx.cu_q, ctx.seqlens_k,
+                                 ctx.n, ctx.num_seqs, ctx.max_q, max_k, H, R, r, self.scale, splits=splits,
+                                 status=ctx.status)                                          # [n, H * R]
+        y = ops.head_products(o.view(n, H, R), self.w_uv)                                    # [n, H, dv]
+        return ops.linear(y.view(n, H * dv), self.w_o)
 
 
 register_mixer("latent_attention", LatentAttention)

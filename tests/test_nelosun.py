@@ -381,18 +381,22 @@ def test_a_far_row_is_found_in_the_shared_cache(dtype):
     """One cached row that matches among hundreds: far back, at page borders, the newest row, with and without split
     keys, for single tokens and portions.  Its latent comes out of every head; a row behind the query does not."""
     from vapi_b200 import ops
-    H, R, r, page = 3, 24, 8, 16
-    for klen, j_star, qlen, splits in ((900, 3, 1, 1), (900, 3, 1, 4), (900, 15, 7, 1), (900, 16, 7, 3), (641, 640, 1, 2), (640, 639, 1, 1),
-                                       (333, 0, 40, 1), (48, 47, 48, 1), (2, 0, 2, 1), (1, 0, 1, 1), (100, 63, 100, 1), (100, 64, 100, 2)):
+    # (widths that are multiples of 16 take the tensor-core kernel in bfloat16, the others the general one)
+    for H, R, r, page in ((3, 24, 8, 16), (5, 32, 16, 16), (2, 128, 32, 64)):
+      for klen, j_star, qlen, splits in ((900, 3, 1, 1), (900, 3, 1, 4), (900, 15, 7, 1), (900, 16, 7, 3), (641, 640, 1, 2), (640, 639, 1, 1),
+                                         (333, 0, 40, 1), (48, 47, 48, 1), (2, 0, 2, 1), (1, 0, 1, 1), (100, 63, 100, 1), (100, 64, 100, 2),
+                                         (130, 31, 99, 1), (130, 32, 99, 1), (97, 96, 33, 2)):
         q, cache, table = nu.planted_latent(klen, j_star, qlen, H, R, r, page, "cuda", dtype)
         out = _shared_attention(ops, q, cache, table, qlen, klen, H, R, r, page, splits, "cuda").float().cpu().view(qlen, H, R)
         for j in range(qlen):
             p = klen - qlen + j
             seen = j_star <= p
-            assert bool(((out[j] - (1.0 if seen else 0.0)).abs() < 0.05).all()), f"keys {klen}, planted {j_star}, query at {p}, splits {splits}"
+            assert bool(((out[j] - (1.0 if seen else 0.0)).abs() < 0.05).all()), \
+                f"heads {H} of {R} + {r}: keys {klen}, planted {j_star}, query at {p}, splits {splits}"
     # against the restatement, at sizes that fit no vector width but four: a mixed batch
     g = torch.Generator().manual_seed(2)
-    for H, R, r, page in ((5, 36, 4, 8), (2, 260, 64, 16), (1, 4, 0, 4), (3, 512, 64, 16)):
+    for H, R, r, page in ((5, 36, 4, 8), (2, 260, 64, 16), (1, 4, 0, 4), (3, 512, 64, 16), (4, 96, 16, 16), (2, 256, 32, 8), (3, 64, 64, 64),
+                          (5, 48, 0, 16), (7, 144, 16, 16)):
         lens, klens = [1, 9, 30, 2], [70, 9, 41, 33]
         pages = sum(-(-k // page) for k in klens)
         cache = (torch.randn((pages + 2, page * (R + r)), generator=g) * 0.5).to(dtype)

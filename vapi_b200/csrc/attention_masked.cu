@@ -15,7 +15,8 @@
 // page holds the key rows alone and a key's value is the first dv elements of its own row (latent attention: the
 // cached latent is both, and the rotated key part follows it in the row); dv <= dk then.
 //
-// bfloat16 with keys and values of one width, 64 or 128, and pages of a multiple of 64 tokens runs on
+// bfloat16 with `shared_kv` and widths that are multiples of 16 (values up to 256) runs on the tensor-core kernel of
+// attention_latent.cuh.  bfloat16 with keys and values of one width, 64 or 128, and pages of a multiple of 64 tokens runs on
 // the tensor cores: the flash kernel of attention_mma.cuh (four warps for prompt portions, one warp
 // per 16 rows and split keys for decode steps) and, for prompt portions of 64 tokens and more at
 // width 64, the tcgen05 kernel of attention_tc.cuh; both take the mask, the sink and the gate as
@@ -29,6 +30,7 @@
 #include "common.cuh"
 #include "attention_mma.cuh"
 #include "attention_tc.cuh"
+#include "attention_latent.cuh"
 
 using namespace vapi;
 
@@ -366,6 +368,18 @@ VAPI_EXPORT int vapi_masked_attention(const void* q, long long q_row_stride, con
         return check_launch("masked_attention_combine",
                             launch(masked_attention_combine_kernel<__nv_bfloat16>, (int)((rows + 3) / 4), 128, 0, stream,
                                    (const float*)part_o, (const float*)part_ml, (const __nv_bfloat16*)gate, gate_stride,
+                                   (__nv_bfloat16*)out, rows, nh, dv, splits));
+    }
+    if (shared_kv && dtype == VAPI_BF16 && !sinks && !gate && window <= 0 && chunk <= 0 &&
+        latent_flash_applies(dk, dv, q_row_stride, q, cache, out)) {
+        // one cached row per token that is key and value at once: the tensor-core kernel of attention_latent.cuh
+        int rc = launch_latent_flash(q, q_row_stride, cache, block_table, table_stride, cu_q, seqlens_k, out, part_o, part_ml,
+                                     num_seqs, max_q, nh, dk, dv, page_size, num_pages, scale, splits, status, stream);
+        if (rc != 0 || splits == 1) return rc;
+        const long long rows = (long long)n * nh;
+        return check_launch("masked_attention_combine",
+                            launch(masked_attention_combine_kernel<__nv_bfloat16>, (int)((rows + 3) / 4), 128, 0, stream,
+                                   (const float*)part_o, (const float*)part_ml, (const __nv_bfloat16*)nullptr, (long long)0,
                                    (__nv_bfloat16*)out, rows, nh, dv, splits));
     }
 #define MA_GO(T, DV) return launch_masked<T, DV>(q, q_row_stride, cache, block_table, table_stride, cu_q, seqlens_k, sinks, gate, \

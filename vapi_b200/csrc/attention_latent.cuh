@@ -7,7 +7,7 @@
 //
 // Work decomposition as in the other flash kernels of the package: the rows of one sequence are its (query token, head)
 // pairs (one kv head: all heads of a token share the keys), cut into tiles of 64; a block of four warps takes one tile,
-// a warp 16 rows of it; keys are walked in tiles of 32 through two shared-memory stages of 16-byte cp.async copies (rows
+// a warp 16 rows of it; keys are walked in tiles of 64 through two shared-memory stages of 16-byte cp.async copies (rows
 // padded by 16 bytes, which makes ldmatrix conflict-free when dk is a multiple of 16); keys no row can see are stored as
 // zeros, so uninitialised cache memory never reaches the arithmetic.  mma.sync m16n8k16, float accumulators; scores,
 // mask, running maximum and sum in float registers; P is rounded to bfloat16 only as the operand of P.V.  With splits >
@@ -22,8 +22,17 @@
 
 namespace vapi {
 
+__device__ __forceinline__ void lf_ldmatrix_x4(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, unsigned a) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(a));
+}
+__device__ __forceinline__ void lf_ldmatrix_x4_trans(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, unsigned a) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(a));
+}
+
 constexpr int LF_ROWS = 64;
-constexpr int LF_BK = 32;
+constexpr int LF_BK = 64;
 constexpr int LF_THREADS = 128;
 
 template <int NTV>
@@ -75,21 +84,27 @@ latent_flash_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride,
     auto load_keys = [&](int it, int stage) {
         __nv_bfloat16* dst = sK + (size_t)stage * LF_BK * ldk;
         const int j0 = it * LF_BK;
-        for (int idx = threadIdx.x; idx < LF_BK * cpr; idx += LF_THREADS) {
-            const int jj = idx / cpr, c = idx - jj * cpr;
+        // a warp takes every fourth row, its lanes the row's 16-byte chunks: one page lookup a row
+        for (int jj = warp; jj < LF_BK; jj += LF_THREADS / 32) {
             const int j = j0 + jj;
-            __nv_bfloat16* d = dst + jj * ldk + c * 8;
+            __nv_bfloat16* d = dst + jj * ldk;
             bool ok = j <= p_max && j < klen;
-            int page = 0;
+            const __nv_bfloat16* src = cache;
             if (ok) {
-                page = bt[j / page_size];
+                const int pi = j / page_size;
+                const int page = bt[pi];
                 if (page < 0 || page >= num_pages) {
-                    if (status) atomicExch(status, 4);
+                    if (lane == 0 && status) atomicExch(status, 4);
                     ok = false;
+                } else {
+                    src = cache + ((size_t)page * page_size + (j - pi * page_size)) * dk;
                 }
             }
-            if (ok) cp_async_16(d, cache + ((size_t)page * page_size + (j % page_size)) * dk + c * 8, 16);
-            else *reinterpret_cast<uint4*>(d) = make_uint4(0u, 0u, 0u, 0u);
+            if (ok) {
+                for (int c = lane; c < cpr; c += 32) cp_async_16(d + c * 8, src + c * 8, 16);
+            } else {
+                for (int c = lane; c < cpr; c += 32) *reinterpret_cast<uint4*>(d + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+            }
         }
     };
 
@@ -109,6 +124,14 @@ latent_flash_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride,
 #pragma unroll
         for (int e = 0; e < 4; ++e) o[i][e] = 0.f;
     const int ksteps = dk >> 4, ntv = dv >> 3;
+    // this lane's ldmatrix addresses (bytes in shared memory), to which the loops add constants
+    const unsigned row_bytes = (unsigned)ldk * 2u;
+    const unsigned aq = (unsigned)__cvta_generic_to_shared(sQ) + (unsigned)(warp * 16 + (lane & 15)) * row_bytes + (unsigned)(lane >> 4) * 16u;
+    const unsigned ak0 = (unsigned)__cvta_generic_to_shared(sK) + (unsigned)((lane & 7) + (lane >> 4) * 8) * row_bytes + (unsigned)((lane >> 3) & 1) * 16u;
+    const unsigned av0 = (unsigned)__cvta_generic_to_shared(sK) + (unsigned)((lane & 7) + ((lane >> 3) & 1) * 8) * row_bytes + (unsigned)(lane >> 4) * 16u;
+    const unsigned stage_bytes = (unsigned)LF_BK * row_bytes;
+    const float scale2 = scale * 1.4426950408889634f;          // scores in units of log 2, so that exp is exp2
+    const int warp_p_min = base_pos + min(tile_start + warp * 16, rows_total - 1) / nh;
 
     if (it_begin < it_end) load_keys(it_begin, 0);
     cp_async_commit();
@@ -118,7 +141,7 @@ latent_flash_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride,
         cp_async_commit();
         cp_async_wait<1>();
         __syncthreads();
-        const __nv_bfloat16* kt = sK + (size_t)stage * LF_BK * ldk;
+        const unsigned ak = ak0 + (unsigned)stage * stage_bytes, av = av0 + (unsigned)stage * stage_bytes;
 
         // ---- scores of 16 rows x 32 keys
         float sc[LF_BK / 8][4];
@@ -128,34 +151,45 @@ latent_flash_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride,
             for (int e = 0; e < 4; ++e) sc[i][e] = 0.f;
         for (int ks = 0; ks < ksteps; ++ks) {
             unsigned a[4];
-            ldmatrix_x4(a[0], a[1], a[2], a[3], sQ + (warp * 16 + (lane & 15)) * ldk + ks * 16 + (lane >> 4) * 8);
+            lf_ldmatrix_x4(a[0], a[1], a[2], a[3], aq + (unsigned)ks * 32u);
 #pragma unroll
             for (int np = 0; np < LF_BK / 16; ++np) {
                 unsigned b0, b1, b2, b3;
-                ldmatrix_x4(b0, b1, b2, b3, kt + (np * 16 + (lane & 7) + (lane >> 4) * 8) * ldk + ks * 16 + ((lane >> 3) & 1) * 8);
+                lf_ldmatrix_x4(b0, b1, b2, b3, ak + (unsigned)np * 16u * row_bytes + (unsigned)ks * 32u);
                 mma_bf16_16816(sc[2 * np], a, b0, b1);
                 mma_bf16_16816(sc[2 * np + 1], a, b2, b3);
             }
         }
         // ---- mask, running maximum and sum
         float mx[2] = {-INFINITY, -INFINITY};
+        if (it * LF_BK + LF_BK - 1 <= warp_p_min && row_ok[1]) {
+            // every key of the tile lies at or before every row of the warp: nothing to mask
 #pragma unroll
-        for (int i = 0; i < LF_BK / 8; ++i)
+            for (int i = 0; i < LF_BK / 8; ++i)
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int h2 = e >> 1;
-                const int j = it * LF_BK + i * 8 + 2 * tq + (e & 1);
-                const bool vis = row_ok[h2] && j <= row_pos[h2] && j < klen;
-                sc[i][e] = vis ? sc[i][e] * scale : -INFINITY;
-                mx[h2] = fmaxf(mx[h2], sc[i][e]);
-            }
+                for (int e = 0; e < 4; ++e) {
+                    sc[i][e] *= scale2;
+                    mx[e >> 1] = fmaxf(mx[e >> 1], sc[i][e]);
+                }
+        } else {
+#pragma unroll
+            for (int i = 0; i < LF_BK / 8; ++i)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int h2 = e >> 1;
+                    const int j = it * LF_BK + i * 8 + 2 * tq + (e & 1);
+                    const bool vis = row_ok[h2] && j <= row_pos[h2] && j < klen;
+                    sc[i][e] = vis ? sc[i][e] * scale2 : -INFINITY;
+                    mx[h2] = fmaxf(mx[h2], sc[i][e]);
+                }
+        }
         float alpha[2];
 #pragma unroll
         for (int h2 = 0; h2 < 2; ++h2) {
             mx[h2] = fmaxf(mx[h2], __shfl_xor_sync(0xffffffffu, mx[h2], 1));
             mx[h2] = fmaxf(mx[h2], __shfl_xor_sync(0xffffffffu, mx[h2], 2));
             const float m_new = fmaxf(m[h2], mx[h2]);
-            alpha[h2] = m_new == -INFINITY ? 1.f : expf(m[h2] - m_new);
+            alpha[h2] = m_new == -INFINITY ? 1.f : exp2f(m[h2] - m_new);
             m[h2] = m_new;
         }
         float rs[2] = {0.f, 0.f};
@@ -166,7 +200,7 @@ latent_flash_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride,
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int h2 = e >> 1;
-                p[e] = sc[i][e] == -INFINITY ? 0.f : expf(sc[i][e] - m[h2]);
+                p[e] = sc[i][e] == -INFINITY ? 0.f : exp2f(sc[i][e] - m[h2]);
                 rs[h2] += p[e];
             }
             pa[i >> 1][(i & 1) * 2] = pack_bf16(p[0], p[1]);
@@ -190,7 +224,7 @@ latent_flash_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride,
             for (int nv = 0; nv < NTV / 2; ++nv) {
                 if (2 * nv < ntv) {
                     unsigned b0, b1, b2, b3;
-                    ldmatrix_x4_trans(b0, b1, b2, b3, kt + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ldk + nv * 16 + (lane >> 4) * 8);
+                    lf_ldmatrix_x4_trans(b0, b1, b2, b3, av + (unsigned)kk * 16u * row_bytes + (unsigned)nv * 32u);
                     mma_bf16_16816(o[2 * nv], pa[kk], b0, b1);
                     mma_bf16_16816(o[2 * nv + 1], pa[kk], b2, b3);
                 }
@@ -223,7 +257,7 @@ latent_flash_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride,
                 if (i < ntv) *reinterpret_cast<float2*>(po + i * 8 + 2 * tq) = make_float2(o[i][2 * h2], o[i][2 * h2 + 1]);
             }
             if (tq == 0) {
-                part_ml[(grow * splits + sp) * 2] = m[h2];
+                part_ml[(grow * splits + sp) * 2] = m[h2] * 0.6931471805599453f;      // back to natural units for the combine
                 part_ml[(grow * splits + sp) * 2 + 1] = l[h2];
             }
         }

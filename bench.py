@@ -144,6 +144,8 @@ def part_tensors(plan):
 
     for call in plan.order:
         yield from of_part(plan.layers[call.layer])
+    for part in getattr(plan, "stream_parts", {}).values():
+        yield from of_part(part)
     yield from of_part(plan.final_norm)
     yield from of_part(plan.head)        # tied: the embedding table, read once by the head
     yield from of_part(plan.embedding)

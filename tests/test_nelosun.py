@@ -36,7 +36,7 @@ def folders(tmp_path_factory):
     return out
 
 
-def _judge(e, slack, dtype, what):
+def _within(e, slack, dtype, what):
     """``e``: errors as parts of the logit range; ``slack``: what reduced precision alone does to the plain model at
     the same positions.  An error counts as far as it exceeds three times that."""
     e, slack = np.asarray(e, dtype=np.float64), np.asarray(slack, dtype=np.float64)
@@ -56,7 +56,7 @@ def _check(runner, oracle, requests, schedule, dtype):
     for rid, toks in requests.items():
         want = oracle.logits(toks)
         e = np.abs(got[rid] - want.numpy()).max(-1) / float(want.max() - want.min())
-        _judge(e, oracle.rounding(toks, dtype), dtype, f"request {rid}")
+        _within(e, oracle.rounding(toks, dtype), dtype, f"request {rid}")
 
 
 def _close(a, b, tol):
@@ -514,4 +514,4 @@ def test_trace_replay_as_a_user_runs_it(dtype, folders, tmp_path):
     where = [(step, i, rid, pos) for step, rows in tr.rows.items() for i, (rid, pos) in enumerate(rows)]
     e = [np.abs(got[step][i] - ref[rid][pos].numpy()).max() / span for step, i, rid, pos in where]
     slack = [oracle.rounding(tokens[rid], dtype)[pos] for _, _, rid, pos in where]
-    _judge(e, slack, dtype, "replay")
+    _within(e, slack, dtype, "replay")

@@ -21,7 +21,7 @@ import json
 import math
 import os
 import struct
-from typing import Any, Dict, List, Optional, Sequence
+from typing import Any, Dict, List, Sequence
 
 import torch
 
